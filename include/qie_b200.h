@@ -41,7 +41,7 @@ typedef uint16_t qie_bf16;     /* raw __nv_bfloat16 bits */
 
 const char* qie_last_error(void);
 /* ABI version; bumped on any signature change. */
-int qie_abi_version(void); /* currently 5 */
+int qie_abi_version(void); /* currently 6 */
 
 /* ------------------------------------------------------------------------------------
  * (1) operator level.  All pointers are DEVICE pointers unless named h_*.
@@ -181,7 +181,13 @@ typedef struct {
   int numerics;          /* QIE_NUMERICS_REFERENCE_ORDER (default) or QIE_NUMERICS_FAST */
   int semantics;         /* QIE_SEMANTICS_REFERENCE (default) or QIE_SEMANTICS_HF */
   float rms_eps;         /* RMSNorm / q,k-norm epsilon; 0 = by semantics (1e-4 reference, 1e-6 HF) */
+  int compute_dtype;     /* QIE_DTYPE_BF16 (default) or QIE_DTYPE_F32 (families with an fp32 path: Nogatar) */
 } qie_engine_opts;
+
+/* BF16: matrix products take bf16 operands with fp32 accumulation, caches hold bf16 rows; what a family defines as fp32
+ * (residual stream, norms, softmax, routers, recurrent state) stays fp32.  F32: everything in IEEE fp32 (no TF32). */
+#define QIE_DTYPE_BF16 0
+#define QIE_DTYPE_F32 1
 
 /* Model semantics.  REFERENCE: what the reference's kernels compute -- interleaved-pair RoPE (src/RoPE.cu:6-22), eps 1e-4
  * (src/normalization.cu:9, src/qk_norm.cu:46).  HF: what the published Qwen2.5 / Qwen3 checkpoints were trained with --
@@ -238,6 +244,18 @@ int qie_engine_create_from_blob(const char* meta_path, void* device_blob, const 
 int qie_engine_create_synthetic(const qie_config* cfg, uint64_t seed, const qie_engine_opts* opts,
                                 qie_engine** out);
 void qie_engine_destroy(qie_engine* e);
+
+/* Model registry: a model folder holds config.json and model.safetensors; the family is chosen by the configuration's
+ * "architecture" (or the first entry of Hugging Face's "architectures").  Registered: "Nogatar" (latent attention /
+ * mLSTM / mixture-of-experts decoder, loaded straight from the safetensors file) and "Qwen2ForCausalLM" /
+ * "Qwen3ForCausalLM" (converted to the blob format in a temporary folder, HF semantics).  qie_model_families returns
+ * the registered architecture names separated by commas; qie_engine_family the name of an engine's family
+ * ("qwen" / "nogatar"). */
+int qie_engine_create_from_dir(const char* model_dir, const qie_engine_opts* opts, qie_engine** out);
+/* The same family over generated weights (measurement, tests): config_json is the text of a config.json. */
+int qie_engine_create_synthetic_json(const char* config_json, uint64_t seed, const qie_engine_opts* opts, qie_engine** out);
+const char* qie_model_families(void);
+const char* qie_engine_family(const qie_engine* e);
 
 /* Tensor parallelism (BASELINE configs[4]; the reference is single-GPU): one
  * process per GPU, every rank creates the engine with the same checkpoint and
@@ -308,6 +326,15 @@ int qie_decode_step(qie_engine* e, const int* h_seqs, const int32_t* h_tokens_in
  * h_tokens_out is HOST int32[steps*n] (step-major). h_tokens_in is the first input. */
 int qie_decode_run(qie_engine* e, const int* h_seqs, const int32_t* h_tokens_in, int n, int steps,
                    int32_t* h_tokens_out);
+
+/* One forward over a batch of entries: entry i feeds the next h_counts[i] tokens of sequence h_seqs[i] (tokens of all
+ * entries back to back in h_tokens), a portion of a prompt or a single decoded token alike; all entries run together.
+ * h_want_rows: indexes into the concatenated token list (ascending) whose logits are copied to h_logits as fp32
+ * [n_want, vocab] (either may be NULL / 0); h_sampled, if given, receives the sampled token of each wanted row.
+ * More rows than max_batch_tokens run as consecutive forwards.  A sequence may appear once.  Families with a
+ * general row forward implement it (Nogatar); others return QIE_EINVAL. */
+int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int* h_counts, const int32_t* h_tokens, int n_want,
+                      const int* h_want_rows, float* h_logits, int32_t* h_sampled);
 
 /* Device-resident variant used for kernel-only timing: token ids stay on the device
  * (the previous step's samples), no host copies, no synchronisation. */

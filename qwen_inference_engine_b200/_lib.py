@@ -32,7 +32,7 @@ class EngineOpts(C.Structure):
                 ("kv_bytes", C.c_size_t), ("max_seqs", C.c_int), ("max_batch_tokens", C.c_int),
                 ("context", C.c_int), ("head_dim_hint", C.c_int), ("use_graph", C.c_int),
                 ("tp_rank", C.c_int), ("tp_size", C.c_int), ("numerics", C.c_int),
-                ("semantics", C.c_int), ("rms_eps", C.c_float)]
+                ("semantics", C.c_int), ("rms_eps", C.c_float), ("compute_dtype", C.c_int)]
 
 
 class KvView(C.Structure):
@@ -93,6 +93,11 @@ def lib():
         "qie_engine_create_from_blob": (i32, [C.c_char_p, vp, C.POINTER(EngineOpts), C.POINTER(vp)]),
         "qie_engine_create_synthetic": (i32, [C.POINTER(Config), u64, C.POINTER(EngineOpts), C.POINTER(vp)]),
         "qie_engine_destroy": (None, [vp]),
+        "qie_engine_create_from_dir": (i32, [C.c_char_p, C.POINTER(EngineOpts), C.POINTER(vp)]),
+        "qie_engine_create_synthetic_json": (i32, [C.c_char_p, u64, C.POINTER(EngineOpts), C.POINTER(vp)]),
+        "qie_model_families": (C.c_char_p, []),
+        "qie_engine_family": (C.c_char_p, [vp]),
+        "qie_forward_batch": (i32, [vp, i32, vp, vp, vp, i32, vp, vp, vp]),
         "qie_tp_plan": (i32, [C.POINTER(Config), i32, i32, ip]),
         "qie_tp_unique_id": (i32, [vp]),
         "qie_engine_tp_connect": (i32, [vp, vp]),

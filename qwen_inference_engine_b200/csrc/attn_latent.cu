@@ -1,0 +1,214 @@
+// attn_latent.cu -- latent (low-rank KV) attention over a paged latent cache (nogatar.h).
+//
+// A cached position holds ONE row shared by all heads: [latent c (rank) | rotated key part (rot)].  With the
+// key up-projection folded into the query (qa_h = [W_uk,h^T q_h | rope(q_rot,h)]) a head's score against position
+// j is qa_h . row_j, and the head's output is W_uv,h (sum_j p_j c_j): attention runs in the latent space and the
+// cache is never expanded to per-head keys and values.  Options: a sliding window, and a per-head softmax sink
+// (one extra term exp(sink_h) in the denominator that carries no value).
+//
+// One CTA per query row: the row's key window is streamed through shared memory in tiles that all heads share;
+// scores, the running maximum / sum and the latent accumulator are fp32.  Keys are always read from the cache
+// (the row's own position was stored by launch_latent_store before), so the result does not depend on how a
+// prompt was cut into forwards or on the other rows of the launch.
+#include "launch.h"
+#include "nogatar.h"
+
+namespace qie {
+namespace {
+
+template <typename T>
+__device__ __forceinline__ float ld_elt(const T* p);
+template <>
+__device__ __forceinline__ float ld_elt<float>(const float* p) { return *p; }
+template <>
+__device__ __forceinline__ float ld_elt<bf16>(const bf16* p) { return bf2f(*p); }
+template <typename T>
+__device__ __forceinline__ void st_elt(T* p, float v);
+template <>
+__device__ __forceinline__ void st_elt<float>(float* p, float v) { *p = v; }
+template <>
+__device__ __forceinline__ void st_elt<bf16>(bf16* p, float v) { *p = f2bf(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+template <typename T>
+__device__ __forceinline__ T* cache_row(const LatentCache& c, const int* block_table, int max_pages, int slot, int pos) {
+  const int page = block_table[(size_t)slot * max_pages + pos / c.page_size];
+  return reinterpret_cast<T*>(c.pool) + (size_t)page * c.page_elems + c.layer_off + (size_t)(pos % c.page_size) * (c.rank + c.rot);
+}
+
+// one CTA per row; 128 threads
+template <typename T>
+__global__ void latent_store_kernel(const LatentCache c, const float* __restrict__ dkv, int ld, const bf16* __restrict__ w_norm, float eps,
+                                    const RopeTable rope, const int* __restrict__ pos, const int* __restrict__ slot,
+                                    const int* __restrict__ block_table, int max_pages) {
+  __shared__ float red[4];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, p = pos[r];
+  const float* src = dkv + (size_t)r * ld;
+  T* dst = cache_row<T>(c, block_table, max_pages, slot[r], p);
+  float s = 0.f;
+  for (int i = threadIdx.x; i < c.rank; i += blockDim.x) s += src[i] * src[i];
+  s = warp_sum(s);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = s;
+  __syncthreads();
+  const float tot = red[0] + red[1] + red[2] + red[3];
+  const float rinv = 1.0f / sqrtf(tot / (float)c.rank + eps);
+  for (int i = threadIdx.x; i < c.rank; i += blockDim.x) st_elt<T>(dst + i, src[i] * rinv * bf2f(w_norm[i]));
+  const int half = rope.dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float cs = rope.cos_t[(size_t)p * half + i], sn = rope.sin_t[(size_t)p * half + i];
+    const float u = src[c.rank + 2 * i], v = src[c.rank + 2 * i + 1];
+    st_elt<T>(dst + c.rank + 2 * i, u * cs - v * sn);
+    st_elt<T>(dst + c.rank + 2 * i + 1, v * cs + u * sn);
+  }
+  for (int i = rope.dims + threadIdx.x; i < c.rot; i += blockDim.x) st_elt<T>(dst + c.rank + i, src[c.rank + i]);
+}
+
+// grid (rows, heads)
+__global__ void rope_heads_kernel(const float* __restrict__ src, int ld_src, int hs_src, float* __restrict__ dst, int ld_dst, int hs_dst, int rot,
+                                  const RopeTable rope, const int* __restrict__ pos) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, h = blockIdx.y, p = pos[r];
+  const float* s = src + (size_t)r * ld_src + (size_t)h * hs_src;
+  float* d = dst + (size_t)r * ld_dst + (size_t)h * hs_dst;
+  const int half = rope.dims / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    const float cs = rope.cos_t[(size_t)p * half + i], sn = rope.sin_t[(size_t)p * half + i];
+    const float u = s[2 * i], v = s[2 * i + 1];
+    d[2 * i] = u * cs - v * sn;
+    d[2 * i + 1] = v * cs + u * sn;
+  }
+  for (int i = rope.dims + threadIdx.x; i < rot; i += blockDim.x) d[i] = s[i];
+}
+
+// Shared memory (floats): qa [H][D] | acc [H][rank] | tile [TK][D+1] | p [H][TK] | m [H] | l [H] | alpha [H]
+template <typename T>
+__global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache c, const float* __restrict__ qa, float* __restrict__ out,
+                                                                const bf16* __restrict__ sink, float scale, int window, int H, int TK,
+                                                                const int* __restrict__ pos, const int* __restrict__ slot,
+                                                                const int* __restrict__ block_table, int max_pages) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_trigger();
+  const int D = c.rank + c.rot, DP = D + 1, R = c.rank;
+  float* s_q = sm;
+  float* s_acc = s_q + (size_t)H * D;
+  float* s_tile = s_acc + (size_t)H * R;
+  float* s_p = s_tile + (size_t)TK * DP;
+  float* s_m = s_p + (size_t)H * TK;
+  float* s_l = s_m + H;
+  float* s_alpha = s_l + H;
+  const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
+  const int p = pos[r], sl = slot[r];
+  const int j_lo = window > 0 ? max(0, p - window + 1) : 0;
+  for (int i = tid; i < H * D; i += nt) s_q[i] = qa[(size_t)r * H * D + i];
+  for (int i = tid; i < H * R; i += nt) s_acc[i] = 0.f;
+  for (int h = tid; h < H; h += nt) {
+    // the sink enters as a key with score sink_h and no value: running maximum sink_h, running sum exp(0) = 1
+    s_m[h] = sink ? bf2f(sink[h]) : -INFINITY;
+    s_l[h] = sink ? 1.f : 0.f;
+  }
+  __syncthreads();
+  for (int j0 = j_lo; j0 <= p; j0 += TK) {
+    const int nk = min(TK, p + 1 - j0);
+    for (int i = tid; i < nk * D; i += nt) {
+      const int jj = i / D, d = i % D;
+      const T* row = cache_row<T>(c, block_table, max_pages, sl, j0 + jj);
+      s_tile[jj * DP + d] = ld_elt<T>(row + d);
+    }
+    __syncthreads();
+    for (int i = tid; i < H * nk; i += nt) {
+      const int h = i / nk, jj = i % nk;
+      const float* q = s_q + (size_t)h * D;
+      const float* k = s_tile + jj * DP;
+      float s = 0.f;
+      for (int d = 0; d < D; ++d) s = fmaf(q[d], k[d], s);
+      s_p[h * TK + jj] = s * scale;
+    }
+    __syncthreads();
+    for (int h = tid >> 5; h < H; h += nt >> 5) {  // one warp per head
+      const int lane = tid & 31;
+      float mx = -INFINITY;
+      for (int jj = lane; jj < nk; jj += 32) mx = fmaxf(mx, s_p[h * TK + jj]);
+      mx = warp_max(mx);
+      const float m_old = s_m[h], m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+      for (int jj = lane; jj < nk; jj += 32) {
+        const float e = expf(s_p[h * TK + jj] - m_new);
+        s_p[h * TK + jj] = e;
+        sum += e;
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) {
+        const float a = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+        s_alpha[h] = a;
+        s_l[h] = s_l[h] * a + sum;
+        s_m[h] = m_new;
+      }
+    }
+    __syncthreads();
+    for (int i = tid; i < H * R; i += nt) {
+      const int h = i / R, d = i % R;
+      float a = s_acc[i] * s_alpha[h];
+      const float* pp = s_p + h * TK;
+      for (int jj = 0; jj < nk; ++jj) a = fmaf(pp[jj], s_tile[jj * DP + d], a);
+      s_acc[i] = a;
+    }
+    __syncthreads();
+  }
+  for (int i = tid; i < H * R; i += nt) out[(size_t)r * H * R + i] = s_acc[i] / s_l[i / R];
+}
+
+size_t attn_smem_floats(int H, int D, int R, int TK) { return (size_t)H * D + (size_t)H * R + (size_t)TK * (D + 1) + (size_t)H * TK + 3 * (size_t)H; }
+
+}  // namespace
+
+cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, const bf16* w_norm, float eps, const RopeTable& rope,
+                                const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  if (c.elt_bytes == 4)
+    return launch_k(latent_store_kernel<float>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages);
+  return launch_k(latent_store_kernel<bf16>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages);
+}
+
+cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,
+                                  const RopeTable& rope, const int* pos, int n, cudaStream_t st) {
+  if (n <= 0 || heads <= 0) return cudaSuccess;
+  return launch_k(rope_heads_kernel, dim3(n, heads), dim3(64), 0, st, src, ld_src, hs_src, dst, ld_dst, hs_dst, rot, rope, pos);
+}
+
+cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
+                                    const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  const int D = c.rank + c.rot;
+  int TK = 128;
+  if (window > 0)
+    while (TK > 8 && TK / 2 >= window) TK /= 2;
+  const size_t budget = 200 * 1024 / sizeof(float);
+  while (TK > 1 && attn_smem_floats(heads, D, c.rank, TK) > budget) TK /= 2;
+  const size_t smem = attn_smem_floats(heads, D, c.rank, TK) * sizeof(float);
+  if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  cudaError_t r;
+  if (c.elt_bytes == 4) {
+    if (smem > 48 * 1024 && (r = cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+      return r;
+    return launch_k(latent_attention_kernel<float>, dim3(n), dim3(256), smem, st, c, qa, out, sink, scale, window, heads, TK, pos, slot, block_table,
+                    max_pages);
+  }
+  if (smem > 48 * 1024 && (r = cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
+    return r;
+  return launch_k(latent_attention_kernel<bf16>, dim3(n), dim3(256), smem, st, c, qa, out, sink, scale, window, heads, TK, pos, slot, block_table,
+                  max_pages);
+}
+
+}  // namespace qie

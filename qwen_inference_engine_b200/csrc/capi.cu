@@ -8,6 +8,7 @@
 #include <string>
 
 #include "engine.h"
+#include "model_registry.h"
 
 using namespace qie;
 
@@ -32,7 +33,7 @@ static int cuda_fail(cudaError_t e, const char* what) {
 extern "C" {
 
 const char* qie_last_error(void) { return g_err; }
-int qie_abi_version(void) { return 5; }
+int qie_abi_version(void) { return 6; }
 
 // ---------------------------------------------------------------- operator level
 int qie_embedding(qie_bf16* out, const qie_bf16* table, const int* ids, size_t hidden, size_t n_tok, qie_stream st) {
@@ -394,6 +395,7 @@ static void engine_free(qie_engine* e) {
     if (kvp.second.exec) cudaGraphExecDestroy(kvp.second.exec);
   for (auto& kvp : e->cap)
     if (kvp.second.d) cudaFree(kvp.second.d);
+  nogatar_free(e);
   if (!e->blob_owned) e->blob = nullptr;
   void* dev[] = {e->blob, e->cos_d, e->sin_d, e->kv.pool, e->block_table_d, e->ids_d, e->pos_d, e->slot_d,
                  e->sampled_d, e->rowstep_d, e->x, e->xn, e->q, e->k, e->v, e->att, e->h, e->logits, e->qkv,
@@ -491,26 +493,10 @@ static int engine_finish_setup(qie_engine* e) {
   e->kv.n_pages = n_pages;
   CU(cudaMalloc(&e->kv.pool, (size_t)n_pages * page_bytes));
   CU(cudaMemsetAsync(e->kv.pool, 0, (size_t)n_pages * page_bytes, e->stream));
-  e->free_pages.resize(n_pages);
-  for (int i = 0; i < n_pages; ++i) e->free_pages[i] = n_pages - 1 - i;  // pop_back hands out 0,1,2,...
-  e->seqs.assign(o.max_seqs, Sequence());
-  e->max_pages_per_seq = std::min(n_pages, (c.context + o.page_size - 1) / o.page_size);
-  size_t bt = (size_t)o.max_seqs * e->max_pages_per_seq;
-  CU(cudaMalloc(&e->block_table_d, bt * sizeof(int)));
-  CU(cudaMemsetAsync(e->block_table_d, 0, bt * sizeof(int), e->stream));
-  CU(cudaMallocHost(&e->block_table_h, bt * sizeof(int)));
-  memset(e->block_table_h, 0, bt * sizeof(int));
-  // row metadata + activations
+  CU(engine_alloc_shared(e, n_pages, c.context));  // page list, sequence slots, block tables, row metadata
+  // activations
   const size_t R = o.max_batch_tokens;
   const size_t H = c.hidden, Dq = (size_t)c.n_q * c.head_dim, Dkv = (size_t)c.n_kv * c.head_dim, I = c.inter;
-  CU(cudaMalloc(&e->ids_d, R * sizeof(int)));
-  CU(cudaMalloc(&e->pos_d, R * sizeof(int)));
-  CU(cudaMalloc(&e->slot_d, R * sizeof(int)));
-  CU(cudaMalloc(&e->sampled_d, R * sizeof(int)));
-  CU(cudaMalloc(&e->rowstep_d, R * sizeof(int)));
-  CU(cudaMallocHost(&e->stage_h, 4 * R * sizeof(int)));
-  e->sampled_h_cap = R;
-  CU(cudaMallocHost(&e->sampled_h, e->sampled_h_cap * sizeof(int)));
   CU(cudaMalloc(&e->x, R * H * sizeof(bf16)));
   CU(cudaMalloc(&e->xn, R * std::max(H, Dq) * sizeof(bf16)));
   CU(cudaMalloc(&e->q, R * Dq * sizeof(bf16)));
@@ -946,6 +932,7 @@ int qie_engine_set_sampling(qie_engine* e, int topk, float temperature_prefill, 
 
 int qie_engine_set_repetition_penalty(qie_engine* e, float penalty) {
   if (!e || !(penalty > 0.0f)) return fail(QIE_EINVAL, "repetition penalty must be > 0");
+  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "repetition penalty");
   if (e->opts.tp_size > 1 && penalty != 1.0f) return fail(QIE_EINVAL, "repetition penalty over a sharded vocabulary is not built");
   CU(cudaSetDevice(e->opts.device));
   CU(cudaStreamSynchronize(e->stream));
@@ -968,6 +955,7 @@ int qie_seq_new(qie_engine* e, int* seq) {
       e->seqs[i] = Sequence();
       e->seqs[i].live = true;
       *seq = i;
+      if (e->ng) nogatar_reset_slot(e, i);  // recurrent state of the slot's previous user
       return QIE_OK;
     }
   return fail(QIE_ENOMEM, "all %zu sequence slots are live", e->seqs.size());
@@ -1030,6 +1018,12 @@ int qie_prefill(qie_engine* e, int seq, const int32_t* h_ids, int n, int32_t* h_
   CU(cudaSetDevice(e->opts.device));
   Sequence& s = e->seqs[seq];
   if (s.host_copy) return fail(QIE_ESTATE, "sequence %d is swapped out (qie_seq_swap_in first)", seq);
+  if (e->ng) {  // families with a general row forward: a prompt is one entry of a batch
+    const int want = n - 1;
+    rc = qie_forward_batch(e, 1, &seq, &n, h_ids, 1, &want, nullptr, h_token);
+    if (rc == QIE_OK) e->seqs[seq].step += 1;
+    return rc;
+  }
   rc = ensure_pages(e, seq, s.len + n);
   if (rc < 0) return rc;
   if (rc) CU(push_block_row(e, seq));
@@ -1063,6 +1057,7 @@ int qie_prefill(qie_engine* e, int seq, const int32_t* h_ids, int n, int32_t* h_
 
 // one decode step for the batch already staged on the device (ids/pos/slot/rowstep)
 static cudaError_t decode_forward(qie_engine* e, int n, int bucket) {
+  if (e->ng) return nogatar_forward(e, n, n, n, e->temp_decode, true);  // one row and one segment per sequence
   if (decode_uses_mega(e, n, bucket)) {
     cudaError_t r = forward_decode_mega(e, n, bucket, e->temp_decode);
     if (r != cudaErrorNotReady) return r;  // NotReady: the cooperative launch could not be placed, nothing ran yet
@@ -1217,6 +1212,7 @@ int qie_sync(qie_engine* e) {
 
 int qie_capture_enable(qie_engine* e, int on) {
   if (!e) return fail(QIE_EINVAL, "null engine");
+  if (e->ng && on) return fail(QIE_EINVAL, "capture: the Nogatar family keeps the residual stream per layer instead (set_int dump_layers)");
   e->capture = on != 0;
   return QIE_OK;
 }
@@ -1240,6 +1236,7 @@ long qie_launch_count(const qie_engine* e) { return e ? e->launches : 0; }
 int qie_seq_swap_out(qie_engine* e, int seq) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
+  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "swap_out");
   Sequence& s = e->seqs[seq];
   if (s.host_copy) return fail(QIE_ESTATE, "sequence %d is already swapped out", seq);
   if (s.pages.empty()) return QIE_OK;
@@ -1259,6 +1256,7 @@ int qie_seq_swap_out(qie_engine* e, int seq) {
 int qie_seq_swap_in(qie_engine* e, int seq) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
+  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "swap_in");
   Sequence& s = e->seqs[seq];
   if (!s.host_copy) return fail(QIE_ESTATE, "sequence %d is not swapped out", seq);
   if ((int)e->free_pages.size() < s.host_pages) return fail(QIE_ENOMEM, "swap_in: %d pages needed, %zu free", s.host_pages, e->free_pages.size());
@@ -1287,6 +1285,7 @@ int qie_seq_swap_in(qie_engine* e, int seq) {
 static int seq_kv_copy(qie_engine* e, int seq, int pos0, int n, qie_bf16* h_K, qie_bf16* h_V, bool write) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
+  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "seq_kv read / write");
   if (n <= 0 || pos0 < 0 || !h_K || !h_V) return fail(QIE_EINVAL, "seq_kv: bad range or null buffers");
   Sequence& s = e->seqs[seq];
   if (s.host_copy) return fail(QIE_ESTATE, "sequence %d is swapped out", seq);
@@ -1337,6 +1336,7 @@ int qie_seq_kv_write(qie_engine* e, int seq, int pos0, int n, const qie_bf16* h_
 int qie_seq_fill_synthetic(qie_engine* e, int seq, int n_pos, uint64_t seed) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
+  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "fill_synthetic");
   if (n_pos <= 0) return fail(QIE_EINVAL, "fill_synthetic: n_pos must be > 0");
   CU(cudaSetDevice(e->opts.device));
   Sequence& s = e->seqs[seq];
@@ -1354,7 +1354,10 @@ int qie_seq_fill_synthetic(qie_engine* e, int seq, int n_pos, uint64_t seed) {
 int qie_engine_set_int(qie_engine* e, const char* key, long value) {
   if (!e || !key) return fail(QIE_EINVAL, "null argument");
   std::string k(key);
-  if (k == "mega") e->use_mega = value != 0;
+  if (k == "dump_layers") {
+    if (!e->ng) return fail(QIE_EINVAL, "dump_layers: Nogatar family only");
+    e->ng->dump_layers = value != 0;
+  } else if (k == "mega") e->use_mega = value != 0;
   else if (k == "gemv") e->use_gemv = value != 0;
   else if (k == "gemv_dataflow") e->gemv_dataflow = value;
   else if (k == "mega_layers_run") e->mega_layers_run = (int)value;
@@ -1392,6 +1395,19 @@ long qie_engine_read_activation(qie_engine* e, const char* name, void* h_out, si
   const size_t R = e->opts.max_batch_tokens;
   const size_t Dq = (size_t)c.n_q * c.head_dim, Dkv = (size_t)c.n_kv * c.head_dim;
   std::string k(name);
+  if (e->ng) {  // "layers": the fp32 residual stream after every layer of the last forward, [layers][max_batch_tokens][width]; "logits_f32"
+    const NgModel* m = e->ng;
+    const void* p = nullptr;
+    size_t nb = 0;
+    if (k == "layers" && m->layer_dump) p = m->layer_dump, nb = m->layers.size() * R * m->width * sizeof(float);
+    else if (k == "logits_f32") p = m->logits, nb = R * (size_t)m->vocab * sizeof(float);
+    else if (k == "sampled") p = e->sampled_d, nb = R * sizeof(int);
+    if (!p) return fail(QIE_EINVAL, "unknown activation %s", name);
+    nb = std::min(nb, max_bytes);
+    CU(cudaStreamSynchronize(e->stream));
+    CU(cudaMemcpy(h_out, p, nb, cudaMemcpyDeviceToHost));
+    return (long)nb;
+  }
   const void* src = nullptr;
   size_t bytes = 0;
   if (k == "x") src = e->x, bytes = R * c.hidden * 2;
@@ -1429,6 +1445,7 @@ int qie_decode_step_profile(qie_engine* e, const int* h_seqs, const int32_t* h_t
                             int* launches_by_kind, int n_kinds) {
   if (!h_tokens_in || !ms_by_kind || !launches_by_kind || n_kinds < KK_COUNT)
     return fail(QIE_EINVAL, "decode_step_profile: need %d kinds", (int)KK_COUNT);
+  if (e && e->ng) return fail(QIE_EINVAL, "decode_step_profile: not available for the Nogatar family");
   int mk = 0;
   int rc = decode_prepare(e, h_seqs, n, &mk);
   if (rc) return rc;
@@ -1459,6 +1476,151 @@ int qie_decode_step_profile(qie_engine* e, const int* h_seqs, const int32_t* h_t
   for (int i = 0; i < n; ++i) {
     e->seqs[h_seqs[i]].len += 1;
     e->seqs[h_seqs[i]].step += 1;
+  }
+  return QIE_OK;
+}
+
+
+// ---------------------------------------------------------------------------------------------------------------
+// model registry + the general batch forward
+const char* qie_model_families(void) { return registry_names(); }
+
+const char* qie_engine_family(const qie_engine* e) { return !e ? "" : (e->ng ? "nogatar" : "qwen"); }
+
+static int create_family(qie_engine* e, int family, const std::string& arg, bool synthetic, uint64_t seed) {
+  if (family != FAMILY_NOGATAR) return fail(QIE_EINVAL, "family not handled here");
+  if (e->opts.tp_size > 1) return fail(QIE_EINVAL, "the Nogatar family is not sharded (tp_size must be 1)");
+  int code = QIE_EIO;
+  const std::string err = synthetic ? nogatar_create_synthetic(e, arg, seed, &code) : nogatar_create(e, arg, &code);
+  if (!err.empty()) return fail(code, "%s", err.c_str());
+  return QIE_OK;
+}
+
+int qie_engine_create_from_dir(const char* model_dir, const qie_engine_opts* opts, qie_engine** out) {
+  if (!model_dir || !out) return fail(QIE_EINVAL, "engine_create_from_dir: null argument");
+  std::string arch, err;
+  const int family = registry_family_of_dir(model_dir, &arch, &err);
+  if (family < 0) return fail(QIE_EIO, "%s", err.c_str());
+  if (family == FAMILY_QWEN) {
+    // Hugging Face checkpoint: convert the shards to the blob format in a temporary folder, then the usual path
+    std::string meta, weights;
+    err = registry_convert_qwen_dir(model_dir, &meta, &weights);
+    if (!err.empty()) return fail(QIE_EIO, "%s", err.c_str());
+    qie_engine_opts o;
+    if (opts) o = *opts;
+    else qie_engine_opts_default(&o);
+    o.semantics = QIE_SEMANTICS_HF;
+    const int rc = qie_engine_create(meta.c_str(), weights.c_str(), &o, out);
+    remove(meta.c_str());
+    remove(weights.c_str());
+    return rc;
+  }
+  qie_engine* e = nullptr;
+  int rc = engine_begin(opts, &e);
+  if (rc) return rc;
+  rc = create_family(e, family, model_dir, false, 0);
+  if (rc) {
+    engine_free(e);
+    return rc;
+  }
+  *out = e;
+  return QIE_OK;
+}
+
+int qie_engine_create_synthetic_json(const char* config_json, uint64_t seed, const qie_engine_opts* opts, qie_engine** out) {
+  if (!config_json || !out) return fail(QIE_EINVAL, "engine_create_synthetic_json: null argument");
+  std::string arch, err;
+  const int family = registry_family_of_config(config_json, &arch, &err);
+  if (family < 0) return fail(QIE_EIO, "%s", err.c_str());
+  if (family != FAMILY_NOGATAR) return fail(QIE_EINVAL, "synthetic weights from a configuration text: Nogatar family (Qwen: qie_engine_create_synthetic)");
+  qie_engine* e = nullptr;
+  int rc = engine_begin(opts, &e);
+  if (rc) return rc;
+  rc = create_family(e, family, config_json, true, seed);
+  if (rc) {
+    engine_free(e);
+    return rc;
+  }
+  *out = e;
+  return QIE_OK;
+}
+
+// Entries -> rows.  Rows of an entry are consecutive positions of its sequence; a forward takes up to
+// max_batch_tokens rows, so a long portion continues in the next forward (the cache and the recurrent state carry it).
+int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int* h_counts, const int32_t* h_tokens, int n_want,
+                      const int* h_want_rows, float* h_logits, int32_t* h_sampled) {
+  if (!e || n_entries <= 0 || !h_seqs || !h_counts || !h_tokens) return fail(QIE_EINVAL, "forward_batch: null argument or empty batch");
+  if (!e->ng) return fail(QIE_EINVAL, "forward_batch: this family has no general row forward (use qie_prefill / qie_decode_step)");
+  if (n_want < 0 || (n_want > 0 && !h_want_rows)) return fail(QIE_EINVAL, "forward_batch: bad want list");
+  CU(cudaSetDevice(e->opts.device));
+  NgModel* m = e->ng;
+  const int R = e->opts.max_batch_tokens;
+  long total = 0;
+  for (int i = 0; i < n_entries; ++i) {
+    int rc = check_seq(e, h_seqs[i]);
+    if (rc) return rc;
+    if (h_counts[i] <= 0) return fail(QIE_EINVAL, "forward_batch: entry %d has no tokens", i);
+    for (int j = 0; j < i; ++j)
+      if (h_seqs[j] == h_seqs[i]) return fail(QIE_EINVAL, "forward_batch: sequence %d appears twice in the batch", h_seqs[i]);
+    for (int t = 0; t < h_counts[i]; ++t) {
+      const int32_t id = h_tokens[total + t];
+      if (id < 0 || id >= e->cfg.vocab) return fail(QIE_EINVAL, "forward_batch: token id %d out of range", id);
+    }
+    total += h_counts[i];
+  }
+  for (int i = 0; i < n_want; ++i)
+    if (h_want_rows[i] < 0 || h_want_rows[i] >= total || (i && h_want_rows[i] <= h_want_rows[i - 1]))
+      return fail(QIE_EINVAL, "forward_batch: want rows must be ascending indexes into the batch's tokens");
+  // pages for everything the batch appends (checked before anything runs)
+  for (int i = 0; i < n_entries; ++i) {
+    int rc = ensure_pages(e, h_seqs[i], e->seqs[h_seqs[i]].len + h_counts[i]);
+    if (rc < 0) return rc;
+    if (rc) CU(push_block_row(e, h_seqs[i]));
+  }
+  e->launches = 0;
+  std::vector<int> seg_start, seg_slot, out_rows;
+  int entry = 0, done_in_entry = 0, want_i = 0;
+  long row0 = 0;  // index of the forward's first row in the batch's token list
+  while (row0 < total) {
+    const int n = (int)std::min<long>(R, total - row0);
+    CU(cudaStreamSynchronize(e->stream));  // staging buffers are reused
+    int* stg = e->stage_h;
+    seg_start.clear(), seg_slot.clear(), out_rows.clear();
+    int r = 0;
+    while (r < n) {
+      const int seq = h_seqs[entry];
+      Sequence& s = e->seqs[seq];
+      const int take = std::min(n - r, h_counts[entry] - done_in_entry);
+      seg_start.push_back(r);
+      seg_slot.push_back(seq);
+      for (int t = 0; t < take; ++t) {
+        stg[r + t] = h_tokens[row0 + r + t];
+        stg[R + r + t] = s.len + t;
+        stg[2 * R + r + t] = seq;
+      }
+      s.len += take;
+      r += take;
+      done_in_entry += take;
+      if (done_in_entry == h_counts[entry]) ++entry, done_in_entry = 0;
+    }
+    seg_start.push_back(n);
+    const int want0 = want_i;
+    while (want_i < n_want && h_want_rows[want_i] < row0 + n) out_rows.push_back((int)(h_want_rows[want_i++] - row0));
+    const int n_out = (int)out_rows.size(), n_seg = (int)seg_slot.size();
+    for (int i = 0; i < n_out; ++i) stg[3 * R + i] = e->seqs[stg[2 * R + out_rows[i]]].step;
+    CU(cudaMemcpyAsync(e->ids_d, stg, n * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->pos_d, stg + R, n * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(e->slot_d, stg + 2 * R, n * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    if (n_out) CU(cudaMemcpyAsync(e->rowstep_d, stg + 3 * R, n_out * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(m->seg_start, seg_start.data(), (n_seg + 1) * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(cudaMemcpyAsync(m->seg_slot, seg_slot.data(), n_seg * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    if (n_out) CU(cudaMemcpyAsync(m->out_rows, out_rows.data(), n_out * sizeof(int), cudaMemcpyHostToDevice, e->stream));
+    CU(nogatar_forward(e, n, n_seg, n_out, e->temp_prefill, false));
+    if (n_out && h_logits)
+      CU(cudaMemcpyAsync(h_logits + (size_t)want0 * e->cfg.vocab, m->logits, (size_t)n_out * e->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
+    if (n_out && h_sampled) CU(cudaMemcpyAsync(h_sampled + want0, e->sampled_d, n_out * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
+    CU(cudaStreamSynchronize(e->stream));  // seg_start / out_rows live on this stack frame's vectors
+    row0 += n;
   }
   return QIE_OK;
 }

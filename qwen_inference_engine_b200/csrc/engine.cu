@@ -16,6 +16,33 @@ bool g_use_pdl = [] {
   return !(v && v[0] == '0');
 }();
 
+cudaError_t engine_alloc_shared(qie_engine* e, int n_pages, int context) {
+  const qie_engine_opts& o = e->opts;
+  cudaError_t r;
+#define SH(expr) \
+  if ((r = (expr)) != cudaSuccess) return r
+  e->free_pages.resize(n_pages);
+  for (int i = 0; i < n_pages; ++i) e->free_pages[i] = n_pages - 1 - i;  // pop_back hands out 0,1,2,...
+  e->seqs.assign(o.max_seqs, Sequence());
+  e->max_pages_per_seq = std::min(n_pages, (context + o.page_size - 1) / o.page_size);
+  const size_t bt = (size_t)o.max_seqs * e->max_pages_per_seq;
+  SH(cudaMalloc(&e->block_table_d, bt * sizeof(int)));
+  SH(cudaMemsetAsync(e->block_table_d, 0, bt * sizeof(int), e->stream));
+  SH(cudaMallocHost(&e->block_table_h, bt * sizeof(int)));
+  memset(e->block_table_h, 0, bt * sizeof(int));
+  const size_t R = o.max_batch_tokens;
+  SH(cudaMalloc(&e->ids_d, R * sizeof(int)));
+  SH(cudaMalloc(&e->pos_d, R * sizeof(int)));
+  SH(cudaMalloc(&e->slot_d, R * sizeof(int)));
+  SH(cudaMalloc(&e->sampled_d, R * sizeof(int)));
+  SH(cudaMalloc(&e->rowstep_d, R * sizeof(int)));
+  SH(cudaMallocHost(&e->stage_h, 4 * R * sizeof(int)));
+  e->sampled_h_cap = R;
+  SH(cudaMallocHost(&e->sampled_h, e->sampled_h_cap * sizeof(int)));
+#undef SH
+  return cudaSuccess;
+}
+
 // launch + count + (optionally) bracket with events for the per-kernel-class timing
 #define QIE_TRY(kind, expr)                                    \
   do {                                                         \

@@ -13,6 +13,7 @@
 
 #include "checkpoint.h"
 #include "kernels.h"
+#include "nogatar.h"
 #include "tp_nccl.h"
 
 namespace qie {
@@ -41,6 +42,9 @@ struct CaptureBuf {
 }  // namespace qie
 
 struct qie_engine {
+  // model family: Qwen (the members below named after its operators) unless `ng` is set (nogatar.h); sequences, pages,
+  // block tables, row metadata, sampling and graphs are shared by the families
+  qie::NgModel* ng = nullptr;
   qie_config cfg{};
   qie_engine_opts opts{};
   int num_sms = 0;
@@ -170,6 +174,9 @@ cudaError_t forward_rows(qie_engine* e, int n_rows, int max_kv_len, int out_row0
 // tensor-parallel forward (per-operator launches, reference-order kernels on the local shard)
 cudaError_t forward_rows_tp(qie_engine* e, int n_rows, int max_kv_len, int out_row0, int n_out, float temperature,
                             bool advance);
+// what every family needs besides its own buffers: the page free list and sequence slots, block tables (device +
+// pinned mirror), row metadata and the pinned staging buffers; sized by e->opts and n_pages
+cudaError_t engine_alloc_shared(qie_engine* e, int n_pages, int context);
 // true if a decode step of n rows / this kv bucket runs through the persistent kernel
 bool decode_uses_mega(const qie_engine* e, int n_rows, int max_kv_len);
 // one decode step (rows described in ids_d/pos_d/slot_d) through the persistent kernel

@@ -1,0 +1,149 @@
+// moe.cu -- routing of a mixture-of-experts feed-forward (nogatar.h): softmax router with top-k choice and
+// renormalised weights, the grouping of (row, choice) assignments by expert for the grouped expert GEMMs
+// (launch_gemm_f32 with grp_off / row_idx), and the weighted combine with an optional gated shared expert.
+// All of it fp32; a row's choice, weights and sums do not depend on the other rows of the launch (its slot in
+// the grouped buffers does, the values stored there do not).
+#include "launch.h"
+#include "nogatar.h"
+
+namespace qie {
+namespace {
+
+// one warp per row; shared memory: per warp `experts` scores
+__global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int experts, int top, int* __restrict__ top_idx,
+                                 float* __restrict__ top_w, int n) {
+  extern __shared__ float sc[];
+  pdl_wait();
+  pdl_trigger();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int r = blockIdx.x * (blockDim.x >> 5) + w;
+  if (r >= n) return;
+  float* s = sc + (size_t)w * experts;
+  const float* zr = z + (size_t)r * ldz;
+  float mx = -INFINITY;
+  for (int e = lane; e < experts; e += 32) mx = fmaxf(mx, zr[e]);
+  for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  float sum = 0.f;
+  for (int e = lane; e < experts; e += 32) {
+    const float v = expf(zr[e] - mx);
+    s[e] = v;
+    sum += v;
+  }
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  __syncwarp();
+  float chosen_sum = 0.f;
+  for (int k = 0; k < top; ++k) {
+    float bv = -1.f;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float v = s[e];
+      if (v > bv) {  // ascending e: the lowest index wins among equals
+        bv = v;
+        bi = e;
+      }
+    }
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > bv || (ov == bv && oi < bi)) {
+        bv = ov;
+        bi = oi;
+      }
+    }
+    const float score = bv / sum;
+    if (lane == 0) {
+      top_idx[(size_t)r * top + k] = bi;
+      top_w[(size_t)r * top + k] = score;
+      s[bi] = -2.f;
+    }
+    chosen_sum += score;
+    __syncwarp();
+  }
+  if (lane == 0) {
+    const float inv = 1.0f / (chosen_sum + 1e-20f);
+    for (int k = 0; k < top; ++k) top_w[(size_t)r * top + k] *= inv;
+  }
+}
+
+// one CTA; warp w serves experts w, w + nw, ...: an ordered compaction of the assignments that chose the expert
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ top_idx, int n_assign, int top, int experts, int* grp_off,
+                                                         int* __restrict__ perm_row, int* __restrict__ slot_of) {
+  pdl_wait();
+  pdl_trigger();
+  const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  for (int e = w; e < experts; e += nw) {
+    int cnt = 0;
+    for (int i0 = 0; i0 < n_assign; i0 += 32) {
+      const int i = i0 + lane;
+      const bool hit = i < n_assign && top_idx[i] == e;
+      cnt += __popc(__ballot_sync(0xffffffffu, hit));
+    }
+    if (lane == 0) grp_off[e + 1] = cnt;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int run = 0;
+    grp_off[0] = 0;
+    for (int e = 0; e < experts; ++e) {
+      run += grp_off[e + 1];
+      grp_off[e + 1] = run;
+    }
+  }
+  __syncthreads();
+  for (int e = w; e < experts; e += nw) {
+    int base = grp_off[e];
+    for (int i0 = 0; i0 < n_assign; i0 += 32) {
+      const int i = i0 + lane;
+      const bool hit = i < n_assign && top_idx[i] == e;
+      const unsigned b = __ballot_sync(0xffffffffu, hit);
+      if (hit) {
+        const int s = base + __popc(b & ((1u << lane) - 1u));
+        perm_row[s] = i / top;
+        slot_of[i] = s;
+      }
+      base += __popc(b);
+    }
+  }
+}
+
+__global__ void moe_combine_kernel(const float* __restrict__ ye, const int* __restrict__ slot_of, const float* __restrict__ top_w, int top,
+                                   const float* __restrict__ ys, const float* __restrict__ z, int ldz, int gate_col, float* __restrict__ y,
+                                   int width) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  float sg = 0.f;
+  if (ys) sg = 1.0f / (1.0f + expf(-z[(size_t)r * ldz + gate_col]));
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    float a = 0.f;
+    for (int k = 0; k < top; ++k) a = fmaf(top_w[(size_t)r * top + k], ye[(size_t)slot_of[(size_t)r * top + k] * width + i], a);
+    if (ys) a = fmaf(sg, ys[(size_t)r * width + i], a);
+    y[(size_t)r * width + i] = a;
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_moe_route(const float* z, int ldz, int experts, int top, int* top_idx, float* top_w, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  int warps = 8;
+  while (warps > 1 && (size_t)warps * experts * sizeof(float) > 40 * 1024) warps /= 2;
+  if ((size_t)warps * experts * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
+  return launch_k(moe_route_kernel, dim3((n + warps - 1) / warps), dim3(32 * warps), (size_t)warps * experts * sizeof(float), st, z, ldz, experts,
+                  top, top_idx, top_w, n);
+}
+
+cudaError_t launch_moe_group(const int* top_idx, int n_assign, int top, int experts, int* grp_off, int* perm_row, int* slot_of, cudaStream_t st) {
+  if (n_assign <= 0) return cudaSuccess;
+  int threads = 32 * experts;
+  threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
+  return launch_k(moe_group_kernel, dim3(1), dim3(threads), 0, st, top_idx, n_assign, top, experts, grp_off, perm_row, slot_of);
+}
+
+cudaError_t launch_moe_combine(const float* ye, const int* slot_of, const float* top_w, int top, const float* ys, const float* z, int ldz,
+                               int gate_col, float* y, int width, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  return launch_k(moe_combine_kernel, dim3(n), dim3(256), 0, st, ye, slot_of, top_w, top, ys, z, ldz, gate_col, y, width);
+}
+
+}  // namespace qie

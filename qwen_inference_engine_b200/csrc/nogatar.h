@@ -1,0 +1,187 @@
+// nogatar.h -- the Nogatar model family: a decoder whose layers mix by latent (low-rank KV) attention with a
+// sliding window and a softmax sink, or by the matrix-memory recurrence of xLSTM (mLSTM), followed by a
+// mixture-of-experts feed-forward; the norm sits on each sublayer's OUTPUT and the residual stream is fp32.
+// The mechanisms are separate launchers with their constants as arguments (ops_f32.cu, attn_latent.cu, mlstm.cu,
+// moe.cu) so that another design can use them; nogatar_model.cu holds the configuration reader, the weight
+// loader and the launch order.  The family shares the engine's sequences, page allocator, block tables, row
+// metadata, sampler, scheduler and C ABI with the Qwen family (engine.h).
+#pragma once
+#include <cuda_runtime.h>
+
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+
+struct qie_engine;
+
+namespace qie {
+
+// ---------------------------------------------------------------- generic fp32-stream operators (ops_f32.cu)
+// C[m, n] = act(sum_k A[m, k] * W[n, k]); fp32 accumulation in ascending k, so a row's result does not depend
+// on which other rows share the launch.  blockIdx.z walks `batches` problems whose operands are `*_batch`
+// elements apart (per-head projections, experts).  With grp_off the rows of problem z are
+// grp_off[z] .. grp_off[z+1]-1 of A / C (M is then the upper bound used for the grid) and row_idx, if given,
+// names the source row of A for each of them (token gather of a mixture of experts).
+struct GemmF32 {
+  const float* A = nullptr;
+  int lda = 0;
+  long a_batch = 0;
+  const bf16* W = nullptr;
+  int ldw = 0;
+  long w_batch = 0;
+  int w_trans = 0;  // 1: W is stored [k, n] (row k, column n) instead of [n, k]
+  float* C = nullptr;
+  int ldc = 0;
+  long c_batch = 0;
+  int M = 0, N = 0, K = 0, batches = 1;
+  const int* grp_off = nullptr;
+  const int* row_idx = nullptr;
+  const bf16* bias = nullptr;  // [N] added before the activation
+  int act = 0;                 // 0 none, 1 relu(z)^2
+  int round_a = 0;             // 1: A is rounded to bf16 before the product (bf16 serving precision)
+  int round_c = 0;             // 1: the result is rounded to bf16 (still stored as fp32)
+};
+cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st);
+// x[r, :] = table[ids[r], :] * scale
+cudaError_t launch_embed_scale_f32(float* x, const bf16* table, const int* ids, int width, int n, float scale, cudaStream_t st);
+// out[r, :] = (res ? res[r, :] : 0) + mult * LN(y[src(r), :]) * w, LN = (y - mean) / sqrt(mean((y - mean)^2) + eps);
+// src(r) = gather ? gather[r] : r.  out may alias res.
+cudaError_t launch_layernorm_f32(const float* y, const bf16* w, float* out, const float* res, const int* gather, int width, int n,
+                                 float eps, float mult, cudaStream_t st);
+// z = cap * tanh(z / cap) in place
+cudaError_t launch_softcap_f32(float* z, size_t n, float cap, cudaStream_t st);
+cudaError_t launch_cast_f32_bf16(const float* in, bf16* out, size_t n, cudaStream_t st);
+
+// ---------------------------------------------------------------- latent attention (attn_latent.cu)
+// Paged latent cache: a page holds page_size positions of every attention layer; layer l's rows are `width`
+// = kv_rank + rot_dim elements ([normed latent | rotated shared key]) starting `layer_off` elements into the page.
+struct LatentCache {
+  void* pool = nullptr;
+  int elt_bytes = 4;  // 4: fp32 rows, 2: bf16 rows
+  int page_size = 0;
+  size_t page_elems = 0;  // elements per page over all layers
+  size_t layer_off = 0;
+  int rank = 0, rot = 0;  // width = rank + rot
+};
+struct RopeTable {
+  const float* cos_t = nullptr;  // [context, dims/2], scaled by the magnitude factor
+  const float* sin_t = nullptr;
+  int dims = 0;  // rotated leading dimensions (pairs (2i, 2i+1))
+};
+// per row: latent = rms_unit(dkv[:rank]) * w_norm, key = rope(dkv[rank:], pos) -> cache row (slot, pos)
+cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, const bf16* w_norm, float eps, const RopeTable& rope,
+                                const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st);
+// rotary positions on src[r, h, 0:rot] -> dst[r, h, 0:rot] (row strides ld_*, head strides hs_*)
+cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,
+                                  const RopeTable& rope, const int* pos, int n, cudaStream_t st);
+// out[r, h, 0:rank] = sum_j p_j * latent_j with p = softmax over the keys j of row r's sequence that satisfy
+// max(0, pos - window + 1) <= j <= pos (window <= 0: all j <= pos) of (qa[r, h, :] . [latent_j | key_j]) * scale;
+// with `sink` the denominator also holds exp(sink[h]).  qa rows are heads * (rank + rot), out rows heads * rank.
+cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
+                                    const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st);
+
+// ---------------------------------------------------------------- mLSTM (mlstm.cu)
+// Recurrent state of one (sequence slot, layer): per head S [dim, vdim], n [dim], m; fp32.
+struct MlstmArgs {
+  const float* qkvg = nullptr;  // [n, 2*heads*dim + 2*heads*vdim]: q | k | v | output gate, head by head
+  int ld = 0;
+  const float* gates = nullptr;  // [n, 2*heads]: input-gate and forget-gate pre-activations (bias added)
+  float* state = nullptr;        // slot s at state + s * slot_stride
+  size_t slot_stride = 0;
+  float* out = nullptr;  // [n, heads*vdim]
+  const bf16* w_norm = nullptr;  // [heads*vdim]
+  int heads = 0, dim = 0, vdim = 0;
+  float gate_cap = 0.f, eps = 0.f;
+  const int* seg_start = nullptr;  // [n_seg + 1] row ranges; rows of a segment are consecutive positions of one sequence
+  const int* seg_slot = nullptr;   // [n_seg]
+  int n_seg = 0;
+};
+inline size_t mlstm_state_floats(int heads, int dim, int vdim) { return (size_t)heads * ((size_t)dim * vdim + dim + 1); }
+cudaError_t launch_mlstm_scan(const MlstmArgs& a, cudaStream_t st);
+
+// ---------------------------------------------------------------- mixture of experts (moe.cu)
+// route: scores = softmax(z[r, 0:experts]); the `top` largest (lowest index first among equals) with weights
+// score / (sum of the chosen + 1e-20).  group: rows sorted by expert: grp_off[experts + 1], perm_row[n*top] (source
+// row of each slot), slot_of[n*top] (slot of assignment (r, k)).  combine: y[r] = sum_k w[r,k] * ye[slot_of[r,k]]
+// (+ sigmoid(z[r, gate_col]) * ys[r] with a shared expert).
+cudaError_t launch_moe_route(const float* z, int ldz, int experts, int top, int* top_idx, float* top_w, int n, cudaStream_t st);
+cudaError_t launch_moe_group(const int* top_idx, int n_assign, int top, int experts, int* grp_off, int* perm_row, int* slot_of, cudaStream_t st);
+cudaError_t launch_moe_combine(const float* ye, const int* slot_of, const float* top_w, int top, const float* ys, const float* z, int ldz,
+                               int gate_col, float* y, int width, int n, cudaStream_t st);
+
+// ---------------------------------------------------------------- the model (nogatar_model.cu)
+struct NgRot {
+  int dims = 0;
+  double base = 10000.0;
+  bool scaled = false;
+  double factor = 1.0, original = 0.0, fast = 0.0, slow = 0.0;
+  bool operator==(const NgRot& o) const {
+    return dims == o.dims && base == o.base && scaled == o.scaled && factor == o.factor && original == o.original && fast == o.fast &&
+           slow == o.slow;
+  }
+};
+struct NgLayer {
+  int type = 0;  // 0 latent_attention, 1 mlstm
+  // mixers
+  int heads = 0, dim = 0, vdim = 0;
+  int rot_dim = 0, kv_rank = 0, window = 0;  // latent attention (window 0 = none)
+  float scale = 1.f;
+  NgRot rot;
+  int rope_id = -1;
+  float gate_cap = 0.f;  // mlstm
+  int state_id = -1, attn_id = -1;
+  // feed-forward (experts 0 = none)
+  int experts = 0, top = 0, ff = 0, shared_ff = 0;
+  // weights (device)
+  const bf16 *norm1 = nullptr, *norm2 = nullptr;
+  const bf16 *wq = nullptr, *wdkv = nullptr, *dkv_norm = nullptr, *wuk = nullptr, *wuv = nullptr, *sink = nullptr, *wo = nullptr;
+  const bf16 *wqkvg = nullptr, *wif = nullptr, *bif = nullptr, *out_norm = nullptr;
+  const bf16 *w_up = nullptr, *w_down = nullptr, *w_router = nullptr, *w_sup = nullptr, *w_sdown = nullptr;
+};
+struct NgModel {
+  int vocab = 0, width = 0;
+  float embed_scale = 1.f, eps = 1e-6f, res_mult = 1.f, softcap = 0.f;
+  std::vector<NgLayer> layers;
+  const bf16 *embed = nullptr, *final_norm = nullptr, *head = nullptr;
+  bf16* blob = nullptr;
+  size_t blob_bytes = 0;
+  bool f32 = false;  // true 32-bit arithmetic everywhere; false: bf16 products / bf16 cache rows
+  // rotary tables, one per distinct configuration
+  std::vector<NgRot> rope_cfg;
+  std::vector<float*> rope_cos, rope_sin;
+  // latent cache
+  void* lat_pool = nullptr;
+  size_t page_elems = 0;
+  std::vector<size_t> lat_off;  // per attention layer
+  // recurrent state: slot s, mlstm layer j at state + s * slot_floats + state_off[j]
+  float* state = nullptr;
+  size_t slot_floats = 0;
+  std::vector<size_t> state_off;
+  // activations (fp32), sized by max_batch_tokens
+  // x: residual stream, y: sublayer output, p0..p3: projections of the mixers, zr/top_*: router, he/ye: expert
+  // hidden and output rows grouped by expert, hs/ys: shared expert, xo: normed output rows
+  float *x = nullptr, *y = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *p3 = nullptr, *zr = nullptr, *top_w = nullptr;
+  float *he = nullptr, *ye = nullptr, *hs = nullptr, *ys = nullptr, *xo = nullptr, *logits = nullptr;
+  int *top_idx = nullptr, *grp_off = nullptr, *perm_row = nullptr, *slot_of = nullptr;
+  int *seg_start = nullptr, *seg_slot = nullptr, *out_rows = nullptr;
+  int* iota = nullptr;  // 0, 1, 2, ...: segments and output rows of a decode step (one row per sequence)
+  int max_experts = 0;
+  bf16* logits_bf = nullptr;
+  // parity hook: residual stream after every layer of the last forward [layers, rows, width]
+  float* layer_dump = nullptr;
+  bool dump_layers = false;
+};
+
+// reads <dir>/config.json and <dir>/model.safetensors; fills e->ng and the engine's shared parts (page pool
+// bookkeeping, block tables, row metadata).  Returns "" or the error text; *code receives the QIE_E* class.
+std::string nogatar_create(qie_engine* e, const std::string& dir, int* code);
+// same model over generated weights (bench / tests): cfg_json is the text of a config.json
+std::string nogatar_create_synthetic(qie_engine* e, const std::string& cfg_json, uint64_t seed, int* code);
+void nogatar_free(qie_engine* e);
+void nogatar_reset_slot(qie_engine* e, int seq);
+// one forward over n rows (ids_d / pos_d / slot_d staged; segments and output rows staged in ng) -> ng->logits
+// [n_out, vocab] and sampled_d[0..n_out)
+cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, float temperature, bool advance);
+
+}  // namespace qie

@@ -1,0 +1,199 @@
+// ops_f32.cu -- operators of models whose residual stream, norms and reductions are fp32 (nogatar.h): scaled
+// embedding gather, output LayerNorm folded into the residual add, a general fp32-accumulate GEMM (batched,
+// grouped, gathered) and the logit soft cap.  Every reduction has a fixed order per row, so a row's result does
+// not depend on the rows it shares a launch with.
+#include "launch.h"
+#include "nogatar.h"
+
+namespace qie {
+namespace {
+
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  // fixed tree: warp shuffles, then warp 0 over the per-warp partials
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = (blockDim.x + 31) >> 5;
+  __syncthreads();  // red may still be read from the previous call
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+  return t;
+}
+
+__global__ void embed_scale_kernel(float* __restrict__ x, const bf16* __restrict__ table, const int* __restrict__ ids, int width,
+                                   float scale) {
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const bf16* src = table + (size_t)ids[r] * width;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) x[(size_t)r * width + i] = bf2f(src[i]) * scale;
+}
+
+__global__ void layernorm_f32_kernel(const float* __restrict__ y, const bf16* __restrict__ w, float* out, const float* res,
+                                     const int* __restrict__ gather, int width, float eps, float mult) {
+  extern __shared__ float row[];
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x;
+  const float* src = y + (size_t)(gather ? gather[r] : r) * width;
+  float s = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = src[i];
+    row[i] = v;
+    s += v;
+  }
+  const float mean = block_sum(s, red) / (float)width;
+  float q = 0.f;
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float d = row[i] - mean;
+    q += d * d;
+  }
+  const float rstd = 1.0f / sqrtf(block_sum(q, red) / (float)width + eps);
+  for (int i = threadIdx.x; i < width; i += blockDim.x) {
+    const float v = (row[i] - mean) * rstd * bf2f(w[i]);
+    const size_t o = (size_t)r * width + i;
+    out[o] = res ? res[o] + mult * v : mult * v;
+  }
+}
+
+constexpr int GT = 64, GK = 16;  // output tile, k step
+
+__global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32 g) {
+  __shared__ float As[GK][GT + 4];
+  __shared__ float Ws[GK][GT + 4];
+  __shared__ int src_row[GT];
+  pdl_wait();
+  pdl_trigger();
+  const int z = blockIdx.z;
+  int row_base = 0, Mz = g.M;
+  if (g.grp_off) {
+    row_base = g.grp_off[z];
+    Mz = g.grp_off[z + 1] - row_base;
+  }
+  const int m0 = blockIdx.y * GT, n0 = blockIdx.x * GT;
+  if (m0 >= Mz) return;
+  const int tid = threadIdx.x;
+  if (tid < GT) {
+    const int m = m0 + tid;
+    int s = -1;
+    if (m < Mz) s = g.row_idx ? g.row_idx[row_base + m] : row_base + m;
+    src_row[tid] = s;
+  }
+  __syncthreads();
+  const float* A = g.A + (size_t)z * g.a_batch;
+  const bf16* W = g.W + (size_t)z * g.w_batch;
+  const int ty = tid >> 4, tx = tid & 15;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < g.K; k0 += GK) {
+    // A tile: 64 rows x 16 k, k fastest
+    for (int i = tid; i < GT * GK; i += 256) {
+      const int mm = i / GK, kk = i % GK;
+      const int s = src_row[mm];
+      float a = 0.f;
+      if (s >= 0 && k0 + kk < g.K) {
+        a = A[(size_t)s * g.lda + k0 + kk];
+        if (g.round_a) a = bf2f(f2bf(a));
+      }
+      As[kk][mm] = a;
+    }
+    if (!g.w_trans) {
+      for (int i = tid; i < GT * GK; i += 256) {
+        const int nn = i / GK, kk = i % GK;
+        float b = 0.f;
+        if (n0 + nn < g.N && k0 + kk < g.K) b = bf2f(W[(size_t)(n0 + nn) * g.ldw + k0 + kk]);
+        Ws[kk][nn] = b;
+      }
+    } else {
+      for (int i = tid; i < GT * GK; i += 256) {
+        const int kk = i / GT, nn = i % GT;
+        float b = 0.f;
+        if (n0 + nn < g.N && k0 + kk < g.K) b = bf2f(W[(size_t)(k0 + kk) * g.ldw + n0 + nn]);
+        Ws[kk][nn] = b;
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < GK; ++kk) {
+      float a[4], b[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) a[i] = As[kk][ty * 4 + i];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) b[j] = Ws[kk][tx * 4 + j];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(a[i], b[j], acc[i][j]);
+    }
+    __syncthreads();
+  }
+  float* C = g.C + (size_t)z * g.c_batch;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= Mz) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n >= g.N) continue;
+      float v = acc[i][j];
+      if (g.bias) v += bf2f(g.bias[n]);
+      if (g.act == 1) {
+        v = fmaxf(v, 0.f);
+        v = v * v;
+      }
+      if (g.round_c) v = bf2f(f2bf(v));
+      C[(size_t)(row_base + m) * g.ldc + n] = v;
+    }
+  }
+}
+
+__global__ void softcap_kernel(float* z, size_t n, float cap) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) z[i] = cap * tanhf(z[i] / cap);
+}
+
+__global__ void cast_f32_bf16_kernel(const float* in, bf16* out, size_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n) out[i] = f2bf(in[i]);
+}
+
+}  // namespace
+
+cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
+  if (g.M <= 0 || g.N <= 0 || g.batches <= 0) return cudaSuccess;
+  dim3 grid((g.N + GT - 1) / GT, (g.M + GT - 1) / GT, g.batches);
+  return launch_k(gemm_f32_kernel, grid, dim3(256), 0, st, g);
+}
+
+cudaError_t launch_embed_scale_f32(float* x, const bf16* table, const int* ids, int width, int n, float scale, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  return launch_k(embed_scale_kernel, dim3(n), dim3(256), 0, st, x, table, ids, width, scale);
+}
+
+cudaError_t launch_layernorm_f32(const float* y, const bf16* w, float* out, const float* res, const int* gather, int width, int n,
+                                 float eps, float mult, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  const size_t smem = (size_t)width * sizeof(float);
+  if (smem > 48 * 1024) {
+    cudaError_t r = cudaFuncSetAttribute(layernorm_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(layernorm_f32_kernel, dim3(n), dim3(256), smem, st, y, w, out, res, gather, width, eps, mult);
+}
+
+cudaError_t launch_softcap_f32(float* z, size_t n, float cap, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  return launch_k(softcap_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, z, n, cap);
+}
+
+cudaError_t launch_cast_f32_bf16(const float* in, bf16* out, size_t n, cudaStream_t st) {
+  if (n == 0) return cudaSuccess;
+  return launch_k(cast_f32_bf16_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, st, in, out, n);
+}
+
+}  // namespace qie

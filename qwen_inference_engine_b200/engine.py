@@ -84,7 +84,11 @@ class Engine:
     def __init__(self, meta_path=None, weights_path=None, *, synthetic=None, seed=1234, device=0,
                  page_size=16, kv_bytes=0, max_pages=0, max_seqs=64, max_batch_tokens=256,
                  context=REF_CONTEXT, use_graph=True, head_dim_hint=0, numerics="reference_order",
-                 tp_rank=0, tp_size=1, semantics="reference", rms_eps=0.0):
+                 tp_rank=0, tp_size=1, semantics="reference", rms_eps=0.0, model_dir=None, config_json=None,
+                 dtype="bfloat16"):
+        """model_dir: a folder with config.json + model.safetensors; the family is chosen by the configuration's
+        architecture (qie_model_families()).  config_json: the same family over generated weights.  dtype "float32"
+        runs families that have an fp32 path in true 32-bit arithmetic."""
         L = _lib.lib()
         o = EngineOpts()
         L.qie_engine_opts_default(C.byref(o))
@@ -94,9 +98,15 @@ class Engine:
         o.numerics = {"reference_order": 0, "fast": 1}[numerics]
         o.tp_rank, o.tp_size = tp_rank, tp_size
         o.semantics, o.rms_eps = {"reference": 0, "hf": 1}[semantics], rms_eps
+        o.compute_dtype = {"bfloat16": 0, "float32": 1}[dtype]
         self.numerics = numerics
         h = C.c_void_p()
-        if synthetic is not None:
+        if model_dir is not None:
+            check(L.qie_engine_create_from_dir(str(model_dir).encode(), C.byref(o), C.byref(h)))
+        elif config_json is not None:
+            text = config_json if isinstance(config_json, str) else __import__("json").dumps(config_json)
+            check(L.qie_engine_create_synthetic_json(text.encode(), seed, C.byref(o), C.byref(h)))
+        elif synthetic is not None:
             cfg = synthetic if isinstance(synthetic, Config) else make_config(synthetic, context=context)
             check(L.qie_engine_create_synthetic(C.byref(cfg), seed, C.byref(o), C.byref(h)))
         else:
@@ -187,6 +197,25 @@ class Engine:
         tok = np.zeros(1, np.int32)
         check(self._L.qie_prefill(self._h, seq, ids.ctypes.data, len(ids), tok.ctypes.data))
         return int(tok[0])
+
+    @property
+    def family(self):
+        return self._L.qie_engine_family(self._h).decode()
+
+    def forward_batch(self, entries, want=(), sample=False):
+        """one forward over [(sequence, tokens), ...]: portions of prompts and single decoded tokens run together.
+        want: indexes into the concatenated token list; returns fp32 logits [len(want), vocab] (and the sampled
+        tokens with sample=True)."""
+        seqs = _i32([s for s, _ in entries])
+        counts = _i32([len(t) for _, t in entries])
+        toks = _i32(np.concatenate([np.asarray(t, np.int32) for _, t in entries]))
+        want = _i32(sorted(want))
+        logits = np.zeros((len(want), self.config.vocab), np.float32)
+        sampled = np.zeros(len(want), np.int32)
+        check(self._L.qie_forward_batch(self._h, len(seqs), seqs.ctypes.data, counts.ctypes.data, toks.ctypes.data, len(want),
+                                        want.ctypes.data if len(want) else None, logits.ctypes.data if len(want) else None,
+                                        sampled.ctypes.data if (sample and len(want)) else None))
+        return (logits, sampled) if sample else logits
 
     def decode_step(self, seqs, tokens_in):
         seqs, tokens_in = _i32(seqs), _i32(tokens_in)
