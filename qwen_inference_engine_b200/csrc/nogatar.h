@@ -52,6 +52,8 @@ cudaError_t launch_layernorm_f32(const float* y, const bf16* w, float* out, cons
 // z = cap * tanh(z / cap) in place
 cudaError_t launch_softcap_f32(float* z, size_t n, float cap, cudaStream_t st);
 cudaError_t launch_cast_f32_bf16(const float* in, bf16* out, size_t n, cudaStream_t st);
+// greedy choice over fp32 rows: out[r] = index of the largest value, the lowest index among equals
+cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, cudaStream_t st);
 
 // ---------------------------------------------------------------- latent attention (attn_latent.cu)
 // Paged latent cache: a page holds page_size positions of every attention layer; layer l's rows are `width`

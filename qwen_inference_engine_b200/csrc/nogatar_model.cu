@@ -557,9 +557,12 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, float te
     NG_TRY(launch_gemm_f32(g, st));
   }
   if (m->softcap > 0.f) NG_TRY(launch_softcap_f32(m->logits, (size_t)n_out * m->vocab, m->softcap, st));
-  // the engine's sampler reads bf16 rows
-  NG_TRY(launch_cast_f32_bf16(m->logits, m->logits_bf, (size_t)n_out * m->vocab, st));
-  NG_TRY(launch_sample_topk(m->logits_bf, e->sampled_d, n_out, m->vocab, temperature, e->topk, e->seed, 0, e->add_step ? e->rowstep_d : nullptr, st));
+  if (e->topk <= 1) {
+    NG_TRY(launch_argmax_f32(m->logits, e->sampled_d, n_out, m->vocab, st));  // greedy on the fp32 logits
+  } else {  // the engine's top-k sampler reads bf16 rows
+    NG_TRY(launch_cast_f32_bf16(m->logits, m->logits_bf, (size_t)n_out * m->vocab, st));
+    NG_TRY(launch_sample_topk(m->logits_bf, e->sampled_d, n_out, m->vocab, temperature, e->topk, e->seed, 0, e->add_step ? e->rowstep_d : nullptr, st));
+  }
   if (advance) NG_TRY(launch_advance(e->pos_d, e->ids_d, e->sampled_d, n_out, e->rowstep_d, st));
   return cudaSuccess;
 }

@@ -162,7 +162,39 @@ __global__ void cast_f32_bf16_kernel(const float* in, bf16* out, size_t n) {
   if (i < n) out[i] = f2bf(in[i]);
 }
 
+// one CTA per row: the largest logit, the lowest index among equals
+__global__ void argmax_f32_kernel(const float* __restrict__ z, int* __restrict__ out, int vocab) {
+  __shared__ float bv[8];
+  __shared__ int bi[8];
+  pdl_wait();
+  pdl_trigger();
+  const float* row = z + (size_t)blockIdx.x * vocab;
+  float v = -INFINITY;
+  int idx = 0x7fffffff;
+  for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
+    const float x = row[i];
+    if (x > v) v = x, idx = i;
+  }
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+    if (ov > v || (ov == v && oi < idx)) v = ov, idx = oi;
+  }
+  if ((threadIdx.x & 31) == 0) bv[threadIdx.x >> 5] = v, bi[threadIdx.x >> 5] = idx;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (bv[w] > v || (bv[w] == v && bi[w] < idx)) v = bv[w], idx = bi[w];
+    out[blockIdx.x] = idx == 0x7fffffff ? 0 : idx;
+  }
+}
+
 }  // namespace
+
+cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, cudaStream_t st) {
+  if (n_rows <= 0) return cudaSuccess;
+  return launch_k(argmax_f32_kernel, dim3(n_rows), dim3(256), 0, st, z, out, vocab);
+}
 
 cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.batches <= 0) return cudaSuccess;
