@@ -404,6 +404,128 @@ def tp_leg(q, torch, np, rank, world, local):
     return out
 
 
+# ---------------------------------------------------------------------------------------------------------------------
+# --family-compare: prefill and decode throughput of the Nogatar family beside the Qwen family at equal size
+# (random weights, layer sizes that resemble a real model's), with a per-kernel-class breakdown of both.
+FAMILY_SIZES = {
+    # width, attention heads / dims, latent rank, window, mLSTM heads / dims, experts / top / ff / shared ff
+    "w1024": dict(width=1024, heads=16, dim=64, rot=32, vdim=64, rank=256, window=512, mh=8, md=64, mvd=128, experts=16, top=2, ff=512, sff=1024),
+    "w2048": dict(width=2048, heads=16, dim=128, rot=64, vdim=128, rank=512, window=1024, mh=8, md=128, mvd=256, experts=32, top=4, ff=512, sff=2048),
+}
+
+
+def nogatar_config(z, vocab=32000):
+    moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["sff"]}}
+    att = {"type": "latent_attention", "mlp": moe,
+           "mixer": {"dim": z["dim"], "heads": z["heads"], "kv_rank": z["rank"], "mask": {"size": z["window"]}, "rot_dim": z["rot"],
+                     "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "fast": 32.0, "original": 1024, "slow": 1.0}},
+                     "scale": (z["dim"] + z["rot"]) ** -0.5, "vdim": z["vdim"]}}
+    rec = {"type": "mlstm", "mlp": moe, "mixer": {"dim": z["md"], "gate_cap": 15.0, "heads": z["mh"], "vdim": z["mvd"]}}
+    return {"architecture": "Nogatar", "embedding": {"scale": 1.0}, "layers": [att, att, rec, att], "logit_softcap": 30.0,
+            "norm": {"eps": 1e-6}, "residual_mult": 0.5, "vocab": vocab, "width": z["width"]}
+
+
+def run_family_compare(args):
+    import numpy as np
+    import torch
+
+    import qwen_inference_engine_b200 as q
+    hbm, src = measured_peaks()
+    try:
+        tpeak = float(json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json")))["bf16_tflops_sustained"])
+    except Exception:
+        tpeak = 1377.7
+    peaks = {"hbm_gbs": hbm, "bf16_tflops_sustained": tpeak, "source": src}
+    T, ctx, steps = args.family_tokens, args.family_ctx, max(8, args.steps)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    out = {"metric": "family_compare_tokens_per_s", "unit": "tokens/s", "n_gpus": 1, "data": "synthetic", "dtype": "bf16",
+           "prefill_tokens": T, "decode_ctx": ctx, "peaks": peaks, "sizes": {}}
+
+    def timed(eng, fn, reps):
+        ext = torch.cuda.ExternalStream(eng.stream)
+        ms = []
+        for i in range(reps + 1):
+            torch.cuda.synchronize()
+            with torch.cuda.stream(ext):
+                e0.record()
+            fn()
+            with torch.cuda.stream(ext):
+                e1.record()
+            torch.cuda.synchronize()
+            if i:
+                ms.append(e0.elapsed_time(e1))
+        return float(np.median(ms))
+
+    def measure(make_engine, vocab, has_fill):
+        res = {}
+        ids = np.random.default_rng(3).integers(0, vocab, size=T, dtype=np.int32)
+        eng = make_engine(T, 2)
+
+        def prefill():
+            s = eng.new_sequence()
+            eng.prefill(s, ids)
+            eng.free_sequence(s)
+        res["prefill_ms"] = timed(eng, prefill, 3)
+        res["prefill_tokens_per_s"] = T / (res["prefill_ms"] / 1e3)
+        eng.profile_begin()
+        prefill()
+        res["prefill_classes_ms"] = {k: round(v[0], 4) for k, v in eng.profile_end().items()}
+        eng.close()
+        for B in (1, 8):
+            eng = make_engine(max(B, 64) if has_fill else ctx, B + 1)
+            seqs, toks = [], []
+            for b in range(B):
+                s = eng.new_sequence()
+                if has_fill:
+                    eng.fill_synthetic(s, ctx, seed=100 + b)
+                    toks.append(1 + b)
+                else:
+                    toks.append(eng.prefill(s, np.random.default_rng(b).integers(0, vocab, size=ctx, dtype=np.int32)))
+                seqs.append(s)
+            cur = eng.decode_run(seqs, toks, 4)[-1]  # warm-up (graph shapes seen and captured)
+            ms = timed(eng, lambda: eng.decode_run(seqs, cur, steps), 2)
+            res[f"decode_b{B}_tokens_per_s"] = B * steps / (ms / 1e3)
+            res[f"decode_b{B}_us_per_step"] = 1e3 * ms / steps
+            if not has_fill or B == 1:
+                try:
+                    eng.profile_begin()
+                    eng.decode_step(seqs, cur)
+                    res[f"decode_b{B}_classes_ms"] = {k: round(v[0], 4) for k, v in eng.profile_end().items()}
+                except Exception as ex:
+                    res[f"decode_b{B}_classes_error"] = str(ex)
+            eng.close()
+        return res
+
+    for name, z in FAMILY_SIZES.items():
+        if args.family_size and name != args.family_size:
+            continue
+        vocab = 32000
+        ng_cfg = json.dumps(nogatar_config(z, vocab))
+        qcfg = q.make_config(dict(hidden=z["width"], inter=z["top"] * z["ff"] + z["sff"], layers=4, n_q=z["width"] // 128, n_kv=2,
+                                  head_dim=128, vocab=vocab), context=8192)
+        pages = (ctx + 64 + 15) // 16 * 9 + (T + 15) // 16 + 8
+        rec = {"nogatar": measure(lambda rows, seqs: q.Engine(config_json=ng_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
+                                                              max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False),
+               "qwen_fast": measure(lambda rows, seqs: q.Engine(synthetic=qcfg, seed=7, numerics="fast", page_size=16, max_pages=pages, max_seqs=seqs,
+                                                                max_batch_tokens=rows, context=8192), vocab, True)}
+        W, L = z["width"], 4
+        # algorithmic work of one token: projections of the mixers + active experts + shared expert (+ head per output row)
+        att = W * (z["heads"] * (z["dim"] + z["rot"]) + z["rank"] + z["rot"]) + z["heads"] * (z["dim"] + z["vdim"]) * z["rank"] + z["heads"] * z["vdim"] * W
+        rec_l = W * (2 * z["mh"] * z["md"] + 2 * z["mh"] * z["mvd"] + 2 * z["mh"]) + z["mh"] * z["mvd"] * W
+        ffn = 2 * W * (z["top"] * z["ff"] + z["sff"]) + W * (z["experts"] + 1)
+        ng_mac = 3 * att + rec_l + L * ffn
+        hq = W
+        qw_mac = L * (2 * hq * hq + 2 * hq * 2 * 128 + 3 * hq * (z["top"] * z["ff"] + z["sff"]))
+        rec["macs_per_token"] = {"nogatar": ng_mac, "qwen": qw_mac}
+        for fam, mac in (("nogatar", ng_mac), ("qwen_fast", qw_mac)):
+            r = rec[fam]
+            r["prefill_tflops"] = 2 * mac * T / (r["prefill_ms"] / 1e3) / 1e12
+            r["prefill_frac_of_tensor_peak"] = r["prefill_tflops"] / peaks["bf16_tflops_sustained"]
+        out["sizes"][name] = rec
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -418,7 +540,15 @@ def main():
     ap.add_argument("--no-fast-extra", action="store_true", help="skip the fast-numerics side measurement")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-extra", action="store_true", help="skip the batch-1 (configs[0]) side measurement")
+    ap.add_argument("--family-compare", action="store_true",
+                    help="side measurement (not the contract line): prefill / decode throughput of the Nogatar family beside the "
+                         "Qwen family at equal size, with per-kernel-class device times")
+    ap.add_argument("--family-size", default="", help="one of " + ", ".join(FAMILY_SIZES) + " (default: all)")
+    ap.add_argument("--family-tokens", type=int, default=2048)
+    ap.add_argument("--family-ctx", type=int, default=1024)
     args = ap.parse_args()
+    if args.family_compare:
+        return run_family_compare(args)
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":

@@ -379,6 +379,11 @@ int qie_seq_fill_synthetic(qie_engine* e, int seq, int n_pos, uint64_t seed);
 int qie_decode_step_profile(qie_engine* e, const int* h_seqs, const int32_t* h_tokens_in, int n, float* ms_by_kind,
                             int* launches_by_kind, int n_kinds);
 const char* qie_kernel_kind_name(int kind);
+/* The same timing around ANY forward of either family: after qie_profile_begin every launch of prefill / decode /
+ * forward_batch calls is bracketed by an event pair (decode steps run eagerly, not from a graph); qie_profile_end sums
+ * device ms and launches per kernel class since begin. */
+int qie_profile_begin(qie_engine* e);
+int qie_profile_end(qie_engine* e, float* ms_by_kind, int* launches_by_kind, int n_kinds);
 
 /* Persistent decode kernel (decode_mega.cu): reference-order decode steps of <= 8 rows run
  * as ONE cooperative launch.  qie_engine_set_int keys: "mega" (0/1, default 1 unless

@@ -132,6 +132,8 @@ def lib():
         "qie_seq_kv_write": (i32, [vp, i32, i32, i32, vp, vp]),
         "qie_decode_step_profile": (i32, [vp, vp, vp, i32, vp, vp, i32]),
         "qie_kernel_kind_name": (C.c_char_p, [i32]),
+        "qie_profile_begin": (i32, [vp]),
+        "qie_profile_end": (i32, [vp, vp, vp, i32]),
         "qie_engine_set_int": (i32, [vp, C.c_char_p, C.c_long]),
         "qie_decode_uses_mega": (i32, [vp, i32, i32]),
         "qie_mega_prof_read": (C.c_long, [vp, vp, sz]),

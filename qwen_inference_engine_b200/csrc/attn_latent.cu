@@ -10,6 +10,8 @@
 // scores, the running maximum / sum and the latent accumulator are fp32.  Keys are always read from the cache
 // (the row's own position was stored by launch_latent_store before), so the result does not depend on how a
 // prompt was cut into forwards or on the other rows of the launch.
+#include <algorithm>
+
 #include "launch.h"
 #include "nogatar.h"
 
@@ -94,13 +96,15 @@ __global__ void rope_heads_kernel(const float* __restrict__ src, int ld_src, int
 // Shared memory (floats): qa [H][D] | acc [H][rank] | tile [TK][D+1] | p [H][TK] | m [H] | l [H] | alpha [H]
 template <typename T>
 __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache c, const float* __restrict__ qa, float* __restrict__ out,
-                                                                const bf16* __restrict__ sink, float scale, int window, int H, int TK,
+                                                                const bf16* __restrict__ sink, float scale, int window, int H_all, int HG, int TK,
                                                                 const int* __restrict__ pos, const int* __restrict__ slot,
-                                                                const int* __restrict__ block_table, int max_pages) {
+                                                                const int* __restrict__ block_table, int max_pages, int n_splits,
+                                                                float* __restrict__ ws) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_trigger();
   const int D = c.rank + c.rot, DP = D + 1, R = c.rank;
+  const int h0 = blockIdx.y * HG, H = min(HG, H_all - h0);  // this CTA's heads
   float* s_q = sm;
   float* s_acc = s_q + (size_t)H * D;
   float* s_tile = s_acc + (size_t)H * R;
@@ -110,21 +114,27 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
   float* s_alpha = s_l + H;
   const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const int p = pos[r], sl = slot[r];
-  const int j_lo = window > 0 ? max(0, p - window + 1) : 0;
-  for (int i = tid; i < H * D; i += nt) s_q[i] = qa[(size_t)r * H * D + i];
+  int j_lo = window > 0 ? max(0, p - window + 1) : 0, j_hi = p;
+  const int split = blockIdx.z;
+  if (n_splits > 1) {  // this CTA's share of the keys, in whole tiles; the sink goes with split 0
+    const int tiles = (p + 1 - j_lo + TK - 1) / TK, per = (tiles + n_splits - 1) / n_splits;
+    j_lo += split * per * TK;
+    j_hi = min(p, j_lo + per * TK - 1);
+  }
+  const bool with_sink = sink && split == 0;
+  for (int i = tid; i < H * D; i += nt) s_q[i] = qa[((size_t)r * H_all + h0) * D + i];
   for (int i = tid; i < H * R; i += nt) s_acc[i] = 0.f;
   for (int h = tid; h < H; h += nt) {
     // the sink enters as a key with score sink_h and no value: running maximum sink_h, running sum exp(0) = 1
-    s_m[h] = sink ? bf2f(sink[h]) : -INFINITY;
-    s_l[h] = sink ? 1.f : 0.f;
+    s_m[h] = with_sink ? bf2f(sink[h0 + h]) : -INFINITY;
+    s_l[h] = with_sink ? 1.f : 0.f;
   }
   __syncthreads();
-  for (int j0 = j_lo; j0 <= p; j0 += TK) {
-    const int nk = min(TK, p + 1 - j0);
-    for (int i = tid; i < nk * D; i += nt) {
-      const int jj = i / D, d = i % D;
+  for (int j0 = j_lo; j0 <= j_hi; j0 += TK) {
+    const int nk = min(TK, j_hi + 1 - j0);
+    for (int jj = tid >> 5; jj < nk; jj += nt >> 5) {  // a warp per cached row: one page lookup, coalesced loads
       const T* row = cache_row<T>(c, block_table, max_pages, sl, j0 + jj);
-      s_tile[jj * DP + d] = ld_elt<T>(row + d);
+      for (int d = tid & 31; d < D; d += 32) s_tile[jj * DP + d] = ld_elt<T>(row + d);
     }
     __syncthreads();
     for (int i = tid; i < H * nk; i += nt) {
@@ -166,7 +176,42 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
     }
     __syncthreads();
   }
-  for (int i = tid; i < H * R; i += nt) out[(size_t)r * H * R + i] = s_acc[i] / s_l[i / R];
+  if (n_splits <= 1) {
+    for (int i = tid; i < H * R; i += nt) out[((size_t)r * H_all + h0) * R + i] = s_acc[i] / s_l[i / R];
+    return;
+  }
+  // partial result of this split: [acc (R) | running maximum | running sum] per (row, head, split)
+  for (int i = tid; i < H * R; i += nt) {
+    const int h = i / R;
+    ws[(((size_t)r * H_all + h0 + h) * n_splits + split) * (R + 2) + i % R] = s_acc[i];
+  }
+  for (int h = tid; h < H; h += nt) {
+    float* w = ws + (((size_t)r * H_all + h0 + h) * n_splits + split) * (R + 2) + R;
+    w[0] = s_m[h];
+    w[1] = s_l[h];
+  }
+}
+
+// grid (rows, heads): out = sum_s acc_s e^(m_s - M) / sum_s l_s e^(m_s - M), splits in ascending order
+__global__ void latent_attention_combine_kernel(const float* __restrict__ ws, float* __restrict__ out, int H, int R, int n_splits) {
+  pdl_wait();
+  pdl_trigger();
+  const float* w = ws + ((size_t)blockIdx.x * H + blockIdx.y) * n_splits * (R + 2);
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, w[(size_t)s * (R + 2) + R]);
+  float den = 0.f;
+  for (int s = 0; s < n_splits; ++s) {
+    const float ms = w[(size_t)s * (R + 2) + R];
+    if (ms != -INFINITY) den += w[(size_t)s * (R + 2) + R + 1] * expf(ms - M);
+  }
+  for (int d = threadIdx.x; d < R; d += blockDim.x) {
+    float a = 0.f;
+    for (int s = 0; s < n_splits; ++s) {
+      const float ms = w[(size_t)s * (R + 2) + R];
+      if (ms != -INFINITY) a = fmaf(w[(size_t)s * (R + 2) + d], expf(ms - M), a);
+    }
+    out[((size_t)blockIdx.x * H + blockIdx.y) * R + d] = a / den;
+  }
 }
 
 size_t attn_smem_floats(int H, int D, int R, int TK) { return (size_t)H * D + (size_t)H * R + (size_t)TK * (D + 1) + (size_t)H * TK + 3 * (size_t)H; }
@@ -188,27 +233,47 @@ cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, floa
 }
 
 cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
-                                    const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st) {
+                                    const int* pos, const int* slot, const int* block_table, int max_pages, int n, int max_keys, float* ws,
+                                    size_t ws_floats, cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
   const int D = c.rank + c.rot;
+  // all heads of a row share the key tiles, so one CTA per row reads them once; with few rows the heads are dealt to
+  // more CTAs (each reads the tiles again, from L2) until the GPU has a CTA per SM or so
+  int HG = heads;
+  while (HG > 1 && (long)n * ((heads + HG - 1) / HG) < 128) HG = (HG + 1) / 2;
   int TK = 128;
   if (window > 0)
     while (TK > 8 && TK / 2 >= window) TK /= 2;
   const size_t budget = 200 * 1024 / sizeof(float);
-  while (TK > 1 && attn_smem_floats(heads, D, c.rank, TK) > budget) TK /= 2;
-  const size_t smem = attn_smem_floats(heads, D, c.rank, TK) * sizeof(float);
+  while (TK > 1 && attn_smem_floats(HG, D, c.rank, TK) > budget) TK /= 2;
+  const size_t smem = attn_smem_floats(HG, D, c.rank, TK) * sizeof(float);
   if (smem > 227 * 1024) return cudaErrorInvalidValue;
+  // few rows and many keys: the key tiles are dealt to several CTAs per (row, head group), then combined
+  const int keys = window > 0 ? std::min(window, max_keys) : max_keys;
+  const int tiles = (keys + TK - 1) / TK;
+  int n_splits = 1;
+  if (ws) {
+    const long ctas = (long)n * ((heads + HG - 1) / HG);
+    while (n_splits < 32 && n_splits < tiles && ctas * n_splits < 256) n_splits *= 2;
+    n_splits = std::min(n_splits, tiles);
+    if ((size_t)n * heads * n_splits * (c.rank + 2) > ws_floats) n_splits = 1;
+  }
+  const dim3 grid(n, (heads + HG - 1) / HG, n_splits);
   cudaError_t r;
   if (c.elt_bytes == 4) {
     if (smem > 48 * 1024 && (r = cudaFuncSetAttribute(latent_attention_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
       return r;
-    return launch_k(latent_attention_kernel<float>, dim3(n), dim3(256), smem, st, c, qa, out, sink, scale, window, heads, TK, pos, slot, block_table,
-                    max_pages);
+    r = launch_k(latent_attention_kernel<float>, grid, dim3(256), smem, st, c, qa, out, sink, scale, window, heads, HG, TK, pos, slot, block_table,
+                    max_pages, n_splits, ws);
+    if (r == cudaSuccess && n_splits > 1) r = launch_k(latent_attention_combine_kernel, dim3(n, heads), dim3(128), 0, st, (const float*)ws, out, heads, c.rank, n_splits);
+    return r;
   }
   if (smem > 48 * 1024 && (r = cudaFuncSetAttribute(latent_attention_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)) != cudaSuccess)
     return r;
-  return launch_k(latent_attention_kernel<bf16>, dim3(n), dim3(256), smem, st, c, qa, out, sink, scale, window, heads, TK, pos, slot, block_table,
-                  max_pages);
+  r = launch_k(latent_attention_kernel<bf16>, grid, dim3(256), smem, st, c, qa, out, sink, scale, window, heads, HG, TK, pos, slot, block_table,
+               max_pages, n_splits, ws);
+  if (r == cudaSuccess && n_splits > 1) r = launch_k(latent_attention_combine_kernel, dim3(n, heads), dim3(128), 0, st, (const float*)ws, out, heads, c.rank, n_splits);
+  return r;
 }
 
 }  // namespace qie

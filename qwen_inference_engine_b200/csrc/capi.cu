@@ -1057,7 +1057,7 @@ int qie_prefill(qie_engine* e, int seq, const int32_t* h_ids, int n, int32_t* h_
 
 // one decode step for the batch already staged on the device (ids/pos/slot/rowstep)
 static cudaError_t decode_forward(qie_engine* e, int n, int bucket) {
-  if (e->ng) return nogatar_forward(e, n, n, n, e->temp_decode, true);  // one row and one segment per sequence
+  if (e->ng) return nogatar_forward(e, n, n, n, bucket, e->temp_decode, true);  // one row and one segment per sequence
   if (decode_uses_mega(e, n, bucket)) {
     cudaError_t r = forward_decode_mega(e, n, bucket, e->temp_decode);
     if (r != cudaErrorNotReady) return r;  // NotReady: the cooperative launch could not be placed, nothing ran yet
@@ -1067,7 +1067,7 @@ static cudaError_t decode_forward(qie_engine* e, int n, int bucket) {
 
 static int decode_launch(qie_engine* e, int n, int max_kv_len) {
   const int bucket = ((max_kv_len + 127) / 128) * 128;
-  if (!e->opts.use_graph || e->capture) {
+  if (!e->opts.use_graph || e->capture || e->prof_on) {
     CU(decode_forward(e, n, bucket));
     return QIE_OK;
   }
@@ -1437,7 +1437,8 @@ long qie_engine_write_activation(qie_engine* e, const char* name, const void* h_
 
 const char* qie_kernel_kind_name(int kind) {
   static const char* names[KK_COUNT] = {"embedding", "rmsnorm", "gemm_qkv", "qkv_post", "attention", "gemm_o",
-                                        "gemm_gateup", "gemm_down", "lm_head", "sample", "advance"};
+                                        "gemm_gateup", "gemm_down", "lm_head", "sample", "advance", "f32_norm", "f32_proj", "latent_store",
+                                        "latent_attn", "mlstm_scan", "moe_route", "moe_experts", "moe_shared", "moe_combine"};
   return kind >= 0 && kind < KK_COUNT ? names[kind] : nullptr;
 }
 
@@ -1586,7 +1587,7 @@ int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int
     CU(cudaStreamSynchronize(e->stream));  // staging buffers are reused
     int* stg = e->stage_h;
     seg_start.clear(), seg_slot.clear(), out_rows.clear();
-    int r = 0;
+    int r = 0, max_kv = 0;
     while (r < n) {
       const int seq = h_seqs[entry];
       Sequence& s = e->seqs[seq];
@@ -1599,6 +1600,7 @@ int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int
         stg[2 * R + r + t] = seq;
       }
       s.len += take;
+      max_kv = std::max(max_kv, s.len);
       r += take;
       done_in_entry += take;
       if (done_in_entry == h_counts[entry]) ++entry, done_in_entry = 0;
@@ -1615,13 +1617,44 @@ int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int
     CU(cudaMemcpyAsync(m->seg_start, seg_start.data(), (n_seg + 1) * sizeof(int), cudaMemcpyHostToDevice, e->stream));
     CU(cudaMemcpyAsync(m->seg_slot, seg_slot.data(), n_seg * sizeof(int), cudaMemcpyHostToDevice, e->stream));
     if (n_out) CU(cudaMemcpyAsync(m->out_rows, out_rows.data(), n_out * sizeof(int), cudaMemcpyHostToDevice, e->stream));
-    CU(nogatar_forward(e, n, n_seg, n_out, e->temp_prefill, false));
+    CU(nogatar_forward(e, n, n_seg, n_out, max_kv, e->temp_prefill, false));
     if (n_out && h_logits)
       CU(cudaMemcpyAsync(h_logits + (size_t)want0 * e->cfg.vocab, m->logits, (size_t)n_out * e->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
     if (n_out && h_sampled) CU(cudaMemcpyAsync(h_sampled + want0, e->sampled_d, n_out * sizeof(int), cudaMemcpyDeviceToHost, e->stream));
     CU(cudaStreamSynchronize(e->stream));  // seg_start / out_rows live on this stack frame's vectors
     row0 += n;
   }
+  return QIE_OK;
+}
+
+
+// Per-kernel-class device timing around ANY forward of either family: begin, run prefill / decode / batch calls
+// (they run eagerly, an event pair around every launch), end sums the classes (names: qie_kernel_kind_name).
+int qie_profile_begin(qie_engine* e) {
+  if (!e) return fail(QIE_EINVAL, "null engine");
+  CU(cudaStreamSynchronize(e->stream));
+  for (auto& r : e->prof) {
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  e->prof.clear();
+  e->prof_on = true;
+  return QIE_OK;
+}
+
+int qie_profile_end(qie_engine* e, float* ms_by_kind, int* launches_by_kind, int n_kinds) {
+  if (!e || !ms_by_kind || !launches_by_kind || n_kinds < KK_COUNT) return fail(QIE_EINVAL, "profile_end: need %d kinds", (int)KK_COUNT);
+  e->prof_on = false;
+  cudaError_t se = cudaStreamSynchronize(e->stream);
+  for (int i = 0; i < n_kinds; ++i) ms_by_kind[i] = 0.f, launches_by_kind[i] = 0;
+  for (auto& r : e->prof) {
+    float ms = 0.f;
+    if (se == cudaSuccess && cudaEventElapsedTime(&ms, r.a, r.b) == cudaSuccess) ms_by_kind[r.kind] += ms, launches_by_kind[r.kind] += 1;
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  e->prof.clear();
+  if (se != cudaSuccess) return cuda_fail(se, "sync (profile)");
   return QIE_OK;
 }
 

@@ -164,7 +164,10 @@ struct qie_engine {
 namespace qie {
 enum KernelKind {
   KK_EMBED = 0, KK_RMSNORM, KK_GEMM_QKV, KK_QKV_POST, KK_ATTN, KK_GEMM_O, KK_GEMM_GATEUP, KK_GEMM_DOWN,
-  KK_LM_HEAD, KK_SAMPLE, KK_ADVANCE, KK_COUNT
+  KK_LM_HEAD, KK_SAMPLE, KK_ADVANCE,
+  // classes of the fp32-stream families (nogatar_model.cu)
+  KK_F32_NORM, KK_F32_PROJ, KK_LATENT_STORE, KK_LATENT_ATTN, KK_MLSTM, KK_MOE_ROUTE, KK_MOE_EXPERTS, KK_MOE_SHARED, KK_MOE_COMBINE,
+  KK_COUNT
 };
 // one forward over n_rows rows already described in ids_d/pos_d/slot_d; logits for rows
 // [out_row0, out_row0+n_out); samples into sampled_d[0..n_out). Returns cudaSuccess or the

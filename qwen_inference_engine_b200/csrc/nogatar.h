@@ -52,6 +52,9 @@ cudaError_t launch_layernorm_f32(const float* y, const bf16* w, float* out, cons
 // z = cap * tanh(z / cap) in place
 cudaError_t launch_softcap_f32(float* z, size_t n, float cap, cudaStream_t st);
 cudaError_t launch_cast_f32_bf16(const float* in, bf16* out, size_t n, cudaStream_t st);
+// operand / result conversion around a bf16 tensor-core GEMM: strided fp32 rows (optionally gathered) <-> dense bf16 rows
+cudaError_t launch_rows_f32_to_bf16(const float* in, int ld_in, const int* row_idx, bf16* out, int cols, int n, cudaStream_t st);
+cudaError_t launch_rows_bf16_to_f32(const bf16* in, int cols, float* out, int ld_out, int act, int n, cudaStream_t st);
 // greedy choice over fp32 rows: out[r] = index of the largest value, the lowest index among equals
 cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, cudaStream_t st);
 
@@ -80,8 +83,11 @@ cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, floa
 // out[r, h, 0:rank] = sum_j p_j * latent_j with p = softmax over the keys j of row r's sequence that satisfy
 // max(0, pos - window + 1) <= j <= pos (window <= 0: all j <= pos) of (qa[r, h, :] . [latent_j | key_j]) * scale;
 // with `sink` the denominator also holds exp(sink[h]).  qa rows are heads * (rank + rot), out rows heads * rank.
+// max_keys bounds pos + 1 over the rows; with a workspace (ws, ws_floats) and few rows the keys of a row are split
+// over several CTAs and combined (needs rows * heads * splits * (rank + 2) floats).
 cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads,
-                                    const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st);
+                                    const int* pos, const int* slot, const int* block_table, int max_pages, int n, int max_keys, float* ws,
+                                    size_t ws_floats, cudaStream_t st);
 
 // ---------------------------------------------------------------- mLSTM (mlstm.cu)
 // Recurrent state of one (sequence slot, layer): per head S [dim, vdim], n [dim], m; fp32.
@@ -167,6 +173,16 @@ struct NgModel {
   float *he = nullptr, *ye = nullptr, *hs = nullptr, *ys = nullptr, *xo = nullptr, *logits = nullptr;
   int *top_idx = nullptr, *grp_off = nullptr, *perm_row = nullptr, *slot_of = nullptr;
   int *seg_start = nullptr, *seg_slot = nullptr, *out_rows = nullptr;
+  // bf16 serving precision, more than 16 rows: projections run on the tcgen05 GEMM (gemm_tcgen05.cu) between two
+  // conversion kernels; ab / cb are its dense bf16 operand and result, tc_maps the weight descriptors by pointer
+  bool use_tc = true;
+  bf16 *ab = nullptr, *cb = nullptr;
+  float* tc_ws = nullptr;
+  size_t tc_ws_bytes = 0;
+  int* tc_counters = nullptr;
+  void* tc_maps = nullptr;  // std::map<const bf16*, TensorMap2D>*
+  float* attn_ws = nullptr;  // partial results of the key-split attention of small batches
+  size_t attn_ws_floats = 0;
   int* iota = nullptr;  // 0, 1, 2, ...: segments and output rows of a decode step (one row per sequence)
   int max_experts = 0;
   bf16* logits_bf = nullptr;
@@ -184,6 +200,7 @@ void nogatar_free(qie_engine* e);
 void nogatar_reset_slot(qie_engine* e, int seq);
 // one forward over n rows (ids_d / pos_d / slot_d staged; segments and output rows staged in ng) -> ng->logits
 // [n_out, vocab] and sampled_d[0..n_out)
-cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, float temperature, bool advance);
+// max_kv_len bounds position + 1 over the rows (grid sizing of the attention)
+cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_kv_len, float temperature, bool advance);
 
 }  // namespace qie

@@ -282,6 +282,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   m->head = P("head");
   e->cfg = qie_config{m->width, 0, (int)m->layers.size(), 0, 0, 0, m->vocab, o.context};
   size_t page_elems = 0, slot_floats = 0;
+  size_t max_rank = 0;
   size_t w0 = 0, w1 = 0, w2 = 0, w3 = 0, w_zr = 1, w_he = 0, w_hs = 0, w_top = 1;
   for (size_t i = 0; i < m->layers.size(); ++i) {
     NgLayer& L = m->layers[i];
@@ -305,6 +306,7 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
       w0 = std::max(w0, H * (d + L.rot_dim) + L.kv_rank + L.rot_dim);
       w1 = std::max(w1, H * (size_t)(L.kv_rank + L.rot_dim));
       w2 = std::max(w2, H * (size_t)L.kv_rank);
+      max_rank = std::max(max_rank, (size_t)L.kv_rank);
       w3 = std::max(w3, H * vd);
     } else {
       L.wqkvg = P(p + "mix.q");
@@ -380,6 +382,22 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   CUS(fbuf(&m->ys, R * W));
   CUS(fbuf(&m->xo, R * W));
   CUS(fbuf(&m->logits, R * (size_t)m->vocab));
+  m->attn_ws_floats = (size_t)4096 * (max_rank + 2);  // up to 4096 (row, head, split) partial results
+  CUS(fbuf(&m->attn_ws, m->attn_ws_floats));
+  if (!m->f32) {
+    size_t maxk = W, maxn = std::max<size_t>(W, (size_t)m->vocab);
+    maxk = std::max(maxk, std::max(w2, std::max(w3, w_hs)));
+    maxn = std::max(maxn, std::max(w0, w_hs));
+    CUS(cudaMalloc(&m->ab, R * maxk * sizeof(bf16)));
+    CUS(cudaMalloc(&m->cb, R * maxn * sizeof(bf16)));
+    m->tc_ws_bytes = (size_t)64 << 20;
+    CUS(cudaMalloc(&m->tc_ws, m->tc_ws_bytes));
+    CUS(cudaMalloc(&m->tc_counters, 8192 * sizeof(int)));
+    CUS(cudaMemsetAsync(m->tc_counters, 0, 8192 * sizeof(int), e->stream));
+    m->tc_maps = new std::map<const bf16*, TensorMap2D>();
+    const char* v = getenv("QIE_NG_TC");
+    m->use_tc = !(v && v[0] == '0');
+  }
   CUS(cudaMalloc(&m->logits_bf, R * (size_t)m->vocab * sizeof(bf16)));
   CUS(cudaMalloc(&m->top_idx, R * w_top * sizeof(int)));
   CUS(cudaMalloc(&m->perm_row, R * w_top * sizeof(int)));
@@ -437,7 +455,8 @@ void nogatar_free(qie_engine* e) {
   if (!m) return;
   void* dev[] = {m->blob, m->lat_pool, m->state, m->x, m->y, m->p0, m->p1, m->p2, m->p3, m->zr, m->top_w, m->he, m->ye, m->hs, m->ys, m->xo,
                  m->logits, m->logits_bf, m->top_idx, m->perm_row, m->slot_of, m->grp_off, m->seg_start, m->seg_slot, m->out_rows, m->iota,
-                 m->layer_dump};
+                 m->layer_dump, m->attn_ws, m->ab, m->cb, m->tc_ws, m->tc_counters};
+  delete static_cast<std::map<const bf16*, TensorMap2D>*>(m->tc_maps);
   for (void* p : dev)
     if (p) cudaFree(p);
   for (float* p : m->rope_cos)
@@ -453,14 +472,71 @@ void nogatar_reset_slot(qie_engine* e, int seq) {
   if (m && m->state) cudaMemsetAsync(m->state + (size_t)seq * m->slot_floats, 0, m->slot_floats * sizeof(float), e->stream);
 }
 
-#define NG_TRY(expr)                     \
-  do {                                   \
-    cudaError_t _e = (expr);             \
-    if (_e != cudaSuccess) return _e;    \
-    ++e->launches;                       \
+
+// C[n, N] = act(A[n, K] W[N, K]^T) on the tcgen05 GEMM: A rows -> dense bf16, result bf16 -> fp32 rows of C.
+// Used in bf16 serving precision for more than 16 rows when the shape fits the kernel's tiles; the operands and the
+// result are the same bf16 values as on the fp32-accumulate path (round_a / round_c), only the summation order differs.
+static bool tc_fits(const NgModel* m, int n, int K, int N, const bf16* W) {
+  return !m->f32 && m->use_tc && m->tc_maps && n > 16 && K >= 64 && K % 64 == 0 && N >= 128 && N % 8 == 0 &&
+         (reinterpret_cast<uintptr_t>(W) & 15) == 0;
+}
+
+static cudaError_t tc_gemm(qie_engine* e, const float* A, int lda, const bf16* W, int K, int N, float* C, int ldc, int act, int n) {
+  NgModel* m = e->ng;
+  cudaStream_t st = e->stream;
+  auto* maps = static_cast<std::map<const bf16*, TensorMap2D>*>(m->tc_maps);
+  auto it = maps->find(W);
+  if (it == maps->end()) {
+    TensorMap2D wm;
+    cudaError_t r = make_tensor_map_2d(&wm, W, N, K, 128);
+    if (r != cudaSuccess) return r;
+    it = maps->emplace(W, wm).first;
+  }
+  cudaError_t r = launch_rows_f32_to_bf16(A, lda, nullptr, m->ab, K, n, st);
+  if (r != cudaSuccess) return r;
+  TensorMap2D xmap;
+  if ((r = make_tensor_map_2d(&xmap, m->ab, n, K, tc_token_tile(n))) != cudaSuccess) return r;
+  TcGemm t{};
+  t.w[0] = &it->second;
+  t.rows[0] = N;
+  t.x = &xmap;
+  t.nseg = 1;
+  t.M = n;
+  t.K = K;
+  t.epi = EPI_STORE;
+  t.out = m->cb;
+  t.ld_out = N;
+  t.ws = m->tc_ws;
+  t.ws_bytes = m->tc_ws_bytes;
+  t.max_splits = (int)std::max<size_t>(1, m->tc_ws_bytes / ((size_t)n * N * sizeof(float)));
+  t.counters = m->tc_counters;
+  t.n_counters = 8192;
+  t.w_static = 0;  // the operand comes from the conversion kernel in front
+  int nl = 0;
+  if ((r = launch_gemm_tcgen05(t, e->num_sms, st, &nl)) != cudaSuccess) return r;
+  e->launches += nl + 1;
+  return launch_rows_bf16_to_f32(m->cb, N, C, ldc, act, n, st);
+}
+
+// launch + count + (when profiling) an event pair per launch, summed per kernel class by qie_profile_end
+#define NG_TRY(kind, expr)                                   \
+  do {                                                       \
+    qie_engine::ProfRec _r{kind, nullptr, nullptr};          \
+    if (e->prof_on) {                                        \
+      cudaEventCreate(&_r.a);                                \
+      cudaEventCreate(&_r.b);                                \
+      cudaEventRecord(_r.a, e->stream);                      \
+    }                                                        \
+    cudaError_t _e = (expr);                                 \
+    if (_e != cudaSuccess) return _e;                        \
+    if (e->prof_on) {                                        \
+      cudaEventRecord(_r.b, e->stream);                      \
+      e->prof.push_back(_r);                                 \
+    }                                                        \
+    ++e->launches;                                           \
   } while (0)
 
-cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, float temperature, bool advance) {
+cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_kv_len, float temperature, bool advance) {
   NgModel* m = e->ng;
   cudaStream_t st = e->stream;
   const int W = m->width;
@@ -474,96 +550,103 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, float te
     g.round_a = round, g.round_c = round;
     return g;
   };
+  // plain projection: the tcgen05 GEMM when the shape and the precision allow, else the fp32-accumulate kernels
+  auto proj = [&](const float* A, int lda, const bf16* Wt, int K, int N, float* C, int ldc, int act, int rows) {
+    if (tc_fits(m, rows, K, N, Wt)) return tc_gemm(e, A, lda, Wt, K, N, C, ldc, act, rows);
+    GemmF32 g = gemm(A, lda, Wt, K, N, C, ldc, act, rnd);
+    g.M = rows;
+    return launch_gemm_f32(g, st);
+  };
   if (m->dump_layers && !m->layer_dump)
     if (cudaMalloc(&m->layer_dump, m->layers.size() * (size_t)e->opts.max_batch_tokens * W * sizeof(float)) != cudaSuccess) return cudaErrorMemoryAllocation;
-  NG_TRY(launch_embed_scale_f32(m->x, m->embed, e->ids_d, W, n, m->embed_scale, st));
+  NG_TRY(KK_EMBED, launch_embed_scale_f32(m->x, m->embed, e->ids_d, W, n, m->embed_scale, st));
   for (size_t li = 0; li < m->layers.size(); ++li) {
     const NgLayer& L = m->layers[li];
     const int H = L.heads, d = L.dim, vd = L.vdim;
     if (L.type == 0) {
       const int r = L.rot_dim, k = L.kv_rank, Nq = H * (d + r), Nd = k + r, ld0 = Nq + Nd, D = k + r;
-      NG_TRY(launch_gemm_f32(gemm(m->x, W, L.wq, W, ld0, m->p0, ld0, 0, rnd), st));
+      NG_TRY(KK_F32_PROJ, proj(m->x, W, L.wq, W, ld0, m->p0, ld0, 0, n));
       LatentCache c;
       c.pool = m->lat_pool, c.elt_bytes = m->f32 ? 4 : 2, c.page_size = e->kv.page_size, c.page_elems = m->page_elems;
       c.layer_off = m->lat_off[L.attn_id], c.rank = k, c.rot = r;
       RopeTable rope{m->rope_cos[L.rope_id], m->rope_sin[L.rope_id], L.rot.dims};
-      NG_TRY(launch_latent_store(c, m->p0 + Nq, ld0, L.dkv_norm, m->eps, rope, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, st));
+      NG_TRY(KK_LATENT_STORE, launch_latent_store(c, m->p0 + Nq, ld0, L.dkv_norm, m->eps, rope, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, st));
       {  // the key up-projection folded into the query: qa[:, h, 0:k] = W_uk,h^T q_h (unrotated part)
         GemmF32 g;
         g.A = m->p0, g.lda = ld0, g.a_batch = d + r;
         g.W = L.wuk, g.ldw = k, g.w_batch = (long)d * k, g.w_trans = 1;
         g.C = m->p1, g.ldc = H * D, g.c_batch = D;
         g.M = n, g.N = k, g.K = d, g.batches = H, g.round_a = rnd;
-        NG_TRY(launch_gemm_f32(g, st));
+        NG_TRY(KK_F32_PROJ, launch_gemm_f32(g, st));
       }
-      if (r > 0) NG_TRY(launch_rope_heads_f32(m->p0 + d, ld0, d + r, m->p1 + k, H * D, D, H, r, rope, e->pos_d, n, st));
-      NG_TRY(launch_latent_attention(c, m->p1, m->p2, L.sink, L.scale, L.window, H, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, st));
+      if (r > 0) NG_TRY(KK_LATENT_STORE, launch_rope_heads_f32(m->p0 + d, ld0, d + r, m->p1 + k, H * D, D, H, r, rope, e->pos_d, n, st));
+      NG_TRY(KK_LATENT_ATTN, launch_latent_attention(c, m->p1, m->p2, L.sink, L.scale, L.window, H, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, max_kv_len, m->attn_ws, m->attn_ws_floats, st));
       {  // value up-projection of the attended latent, head by head
         GemmF32 g;
         g.A = m->p2, g.lda = H * k, g.a_batch = k;
         g.W = L.wuv, g.ldw = k, g.w_batch = (long)vd * k;
         g.C = m->p3, g.ldc = H * vd, g.c_batch = vd;
         g.M = n, g.N = vd, g.K = k, g.batches = H, g.round_a = rnd, g.round_c = rnd;
-        NG_TRY(launch_gemm_f32(g, st));
+        NG_TRY(KK_F32_PROJ, launch_gemm_f32(g, st));
       }
-      NG_TRY(launch_gemm_f32(gemm(m->p3, H * vd, L.wo, H * vd, W, m->y, W, 0, rnd), st));
+      NG_TRY(KK_F32_PROJ, proj(m->p3, H * vd, L.wo, H * vd, W, m->y, W, 0, n));
     } else {
       const int N0 = 2 * H * d + 2 * H * vd;
-      NG_TRY(launch_gemm_f32(gemm(m->x, W, L.wqkvg, W, N0, m->p0, N0, 0, rnd), st));
+      NG_TRY(KK_F32_PROJ, proj(m->x, W, L.wqkvg, W, N0, m->p0, N0, 0, n));
       {
         GemmF32 g = gemm(m->x, W, L.wif, W, 2 * H, m->p1, 2 * H, 0, 0);  // gate pre-activations: fp32
         g.bias = L.bif;
-        NG_TRY(launch_gemm_f32(g, st));
+        NG_TRY(KK_F32_PROJ, launch_gemm_f32(g, st));
       }
       MlstmArgs a;
       a.qkvg = m->p0, a.ld = N0, a.gates = m->p1;
       a.state = m->state + m->state_off[L.state_id], a.slot_stride = m->slot_floats;
       a.out = m->p2, a.w_norm = L.out_norm, a.heads = H, a.dim = d, a.vdim = vd, a.gate_cap = L.gate_cap, a.eps = m->eps;
       a.seg_start = seg_start, a.seg_slot = seg_slot, a.n_seg = n_seg;
-      NG_TRY(launch_mlstm_scan(a, st));
-      NG_TRY(launch_gemm_f32(gemm(m->p2, H * vd, L.wo, H * vd, W, m->y, W, 0, rnd), st));
+      NG_TRY(KK_MLSTM, launch_mlstm_scan(a, st));
+      NG_TRY(KK_F32_PROJ, proj(m->p2, H * vd, L.wo, H * vd, W, m->y, W, 0, n));
     }
-    NG_TRY(launch_layernorm_f32(m->y, L.norm1, m->x, m->x, nullptr, W, n, m->eps, m->res_mult, st));
+    NG_TRY(KK_F32_NORM, launch_layernorm_f32(m->y, L.norm1, m->x, m->x, nullptr, W, n, m->eps, m->res_mult, st));
     if (L.experts > 0) {
       const int E = L.experts, top = L.top, ldz = E + (L.shared_ff > 0 ? 1 : 0);
-      NG_TRY(launch_gemm_f32(gemm(m->x, W, L.w_router, W, ldz, m->zr, ldz, 0, 0), st));  // router (+ shared gate): fp32
-      NG_TRY(launch_moe_route(m->zr, ldz, E, top, m->top_idx, m->top_w, n, st));
-      NG_TRY(launch_moe_group(m->top_idx, n * top, top, E, m->grp_off, m->perm_row, m->slot_of, st));
+      NG_TRY(KK_MOE_ROUTE, launch_gemm_f32(gemm(m->x, W, L.w_router, W, ldz, m->zr, ldz, 0, 0), st));  // router (+ shared gate): fp32
+      NG_TRY(KK_MOE_ROUTE, launch_moe_route(m->zr, ldz, E, top, m->top_idx, m->top_w, n, st));
+      NG_TRY(KK_MOE_ROUTE, launch_moe_group(m->top_idx, n * top, top, E, m->grp_off, m->perm_row, m->slot_of, st));
       {
         GemmF32 g = gemm(m->x, W, L.w_up, W, L.ff, m->he, L.ff, 1, rnd);
         g.M = n * top, g.batches = E, g.w_batch = (long)L.ff * W, g.grp_off = m->grp_off, g.row_idx = m->perm_row;
-        NG_TRY(launch_gemm_f32(g, st));
+        NG_TRY(KK_MOE_EXPERTS, launch_gemm_f32(g, st));
         GemmF32 g2 = gemm(m->he, L.ff, L.w_down, L.ff, W, m->ye, W, 0, rnd);
         g2.M = n * top, g2.batches = E, g2.w_batch = (long)W * L.ff, g2.grp_off = m->grp_off;
-        NG_TRY(launch_gemm_f32(g2, st));
+        NG_TRY(KK_MOE_EXPERTS, launch_gemm_f32(g2, st));
       }
       if (L.shared_ff > 0) {
-        NG_TRY(launch_gemm_f32(gemm(m->x, W, L.w_sup, W, L.shared_ff, m->hs, L.shared_ff, 1, rnd), st));
-        NG_TRY(launch_gemm_f32(gemm(m->hs, L.shared_ff, L.w_sdown, L.shared_ff, W, m->ys, W, 0, rnd), st));
+        NG_TRY(KK_MOE_SHARED, proj(m->x, W, L.w_sup, W, L.shared_ff, m->hs, L.shared_ff, 1, n));
+        NG_TRY(KK_MOE_SHARED, proj(m->hs, L.shared_ff, L.w_sdown, L.shared_ff, W, m->ys, W, 0, n));
       }
-      NG_TRY(launch_moe_combine(m->ye, m->slot_of, m->top_w, top, L.shared_ff > 0 ? m->ys : nullptr, m->zr, ldz, E, m->y, W, n, st));
-      NG_TRY(launch_layernorm_f32(m->y, L.norm2, m->x, m->x, nullptr, W, n, m->eps, m->res_mult, st));
+      NG_TRY(KK_MOE_COMBINE, launch_moe_combine(m->ye, m->slot_of, m->top_w, top, L.shared_ff > 0 ? m->ys : nullptr, m->zr, ldz, E, m->y, W, n, st));
+      NG_TRY(KK_F32_NORM, launch_layernorm_f32(m->y, L.norm2, m->x, m->x, nullptr, W, n, m->eps, m->res_mult, st));
     }
     if (m->dump_layers)
       if (cudaMemcpyAsync(m->layer_dump + li * (size_t)e->opts.max_batch_tokens * W, m->x, (size_t)n * W * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)
         return cudaErrorUnknown;
   }
   if (n_out <= 0) return cudaSuccess;
-  NG_TRY(launch_layernorm_f32(m->x, m->final_norm, m->xo, nullptr, out_rows, W, n_out, m->eps, 1.0f, st));
+  NG_TRY(KK_F32_NORM, launch_layernorm_f32(m->x, m->final_norm, m->xo, nullptr, out_rows, W, n_out, m->eps, 1.0f, st));
   {
     GemmF32 g = gemm(m->xo, W, m->head, W, m->vocab, m->logits, m->vocab, 0, rnd);
     g.M = n_out;
     g.round_c = 0;
-    NG_TRY(launch_gemm_f32(g, st));
+    NG_TRY(KK_LM_HEAD, launch_gemm_f32(g, st));
   }
-  if (m->softcap > 0.f) NG_TRY(launch_softcap_f32(m->logits, (size_t)n_out * m->vocab, m->softcap, st));
+  if (m->softcap > 0.f) NG_TRY(KK_LM_HEAD, launch_softcap_f32(m->logits, (size_t)n_out * m->vocab, m->softcap, st));
   if (e->topk <= 1) {
-    NG_TRY(launch_argmax_f32(m->logits, e->sampled_d, n_out, m->vocab, st));  // greedy on the fp32 logits
+    NG_TRY(KK_SAMPLE, launch_argmax_f32(m->logits, e->sampled_d, n_out, m->vocab, st));  // greedy on the fp32 logits
   } else {  // the engine's top-k sampler reads bf16 rows
-    NG_TRY(launch_cast_f32_bf16(m->logits, m->logits_bf, (size_t)n_out * m->vocab, st));
-    NG_TRY(launch_sample_topk(m->logits_bf, e->sampled_d, n_out, m->vocab, temperature, e->topk, e->seed, 0, e->add_step ? e->rowstep_d : nullptr, st));
+    NG_TRY(KK_SAMPLE, launch_cast_f32_bf16(m->logits, m->logits_bf, (size_t)n_out * m->vocab, st));
+    NG_TRY(KK_SAMPLE, launch_sample_topk(m->logits_bf, e->sampled_d, n_out, m->vocab, temperature, e->topk, e->seed, 0, e->add_step ? e->rowstep_d : nullptr, st));
   }
-  if (advance) NG_TRY(launch_advance(e->pos_d, e->ids_d, e->sampled_d, n_out, e->rowstep_d, st));
+  if (advance) NG_TRY(KK_ADVANCE, launch_advance(e->pos_d, e->ids_d, e->sampled_d, n_out, e->rowstep_d, st));
   return cudaSuccess;
 }
 

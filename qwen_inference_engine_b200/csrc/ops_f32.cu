@@ -58,6 +58,7 @@ __global__ void layernorm_f32_kernel(const float* __restrict__ y, const bf16* __
 }
 
 constexpr int GT = 64, GK = 16;  // output tile, k step
+constexpr int GEMV_MAX_ROWS = 16;  // up to this many rows (per launch, over all groups) the warp-per-column kernels run
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32 g) {
   __shared__ float As[GK][GT + 4];
@@ -148,6 +149,101 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32 g) {
   }
 }
 
+
+// Few rows (decode steps, lightly loaded experts): one warp per output column streams the weight row with 16-byte
+// loads and keeps up to 8 rows of partial sums; experts without rows leave at once, so a mixture of experts reads
+// only the chosen experts' weights.  The k order per output is fixed (lane-strided, then a shuffle tree), whatever
+// the number of rows.
+template <bool VEC>
+__global__ void __launch_bounds__(256) gemv_f32_kernel(const GemmF32 g) {
+  pdl_wait();
+  pdl_trigger();
+  const int z = blockIdx.z;
+  int row_base = 0, Mz = g.M;
+  if (g.grp_off) {
+    row_base = g.grp_off[z];
+    Mz = g.grp_off[z + 1] - row_base;
+  }
+  const int n = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (Mz <= 0 || n >= g.N) return;
+  const float* A = g.A + (size_t)z * g.a_batch;
+  const bf16* w = g.W + (size_t)z * g.w_batch + (size_t)n * g.ldw;
+  float* C = g.C + (size_t)z * g.c_batch;
+  for (int m0 = 0; m0 < Mz; m0 += 8) {
+    const int mr = min(8, Mz - m0);
+    const float* arow[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const int m = m0 + min(i, mr - 1);
+      arow[i] = A + (size_t)(g.row_idx ? g.row_idx[row_base + m] : row_base + m) * g.lda;
+    }
+    float acc[8] = {};
+    if (VEC) {
+      for (int k = lane * 8; k < g.K; k += 256) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(w + k);
+        const float wf[8] = {lo2f(wv.x), hi2f(wv.x), lo2f(wv.y), hi2f(wv.y), lo2f(wv.z), hi2f(wv.z), lo2f(wv.w), hi2f(wv.w)};
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (i < mr) {
+            const float4 a0 = *reinterpret_cast<const float4*>(arow[i] + k), a1 = *reinterpret_cast<const float4*>(arow[i] + k + 4);
+            float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              if (g.round_a) av[j] = bf2f(f2bf(av[j]));
+              acc[i] = fmaf(av[j], wf[j], acc[i]);
+            }
+          }
+        }
+      }
+    } else {
+      for (int k = lane; k < g.K; k += 32) {
+        const float wf = bf2f(w[k]);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          if (i < mr) {
+            float a = arow[i][k];
+            if (g.round_a) a = bf2f(f2bf(a));
+            acc[i] = fmaf(a, wf, acc[i]);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      for (int o = 16; o > 0; o >>= 1) acc[i] += __shfl_xor_sync(0xffffffffu, acc[i], o);
+    if (lane == 0) {
+      for (int i = 0; i < mr; ++i) {
+        float v = acc[i];
+        if (g.bias) v += bf2f(g.bias[n]);
+        if (g.act == 1) {
+          v = fmaxf(v, 0.f);
+          v = v * v;
+        }
+        if (g.round_c) v = bf2f(f2bf(v));
+        C[(size_t)(row_base + m0 + i) * g.ldc + n] = v;
+      }
+    }
+  }
+}
+
+// the same for W stored [k, n]: one thread per output column (coalesced over n), k ascending
+__global__ void gemv_trans_f32_kernel(const GemmF32 g) {
+  pdl_wait();
+  pdl_trigger();
+  const int z = blockIdx.z, m = blockIdx.y, n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= g.N) return;
+  const float* a = g.A + (size_t)z * g.a_batch + (size_t)m * g.lda;
+  const bf16* w = g.W + (size_t)z * g.w_batch + n;
+  float acc = 0.f;
+  for (int k = 0; k < g.K; ++k) {
+    float av = a[k];
+    if (g.round_a) av = bf2f(f2bf(av));
+    acc = fmaf(av, bf2f(w[(size_t)k * g.ldw]), acc);
+  }
+  if (g.round_c) acc = bf2f(f2bf(acc));
+  g.C[(size_t)z * g.c_batch + (size_t)m * g.ldc + n] = acc;
+}
+
 __global__ void softcap_kernel(float* z, size_t n, float cap) {
   pdl_wait();
   pdl_trigger();
@@ -160,6 +256,31 @@ __global__ void cast_f32_bf16_kernel(const float* in, bf16* out, size_t n) {
   pdl_trigger();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) out[i] = f2bf(in[i]);
+}
+
+// rows of a strided fp32 matrix -> dense bf16 rows (operand of a tensor-core GEMM); with row_idx a gather
+__global__ void rows_f32_to_bf16_kernel(const float* __restrict__ in, int ld_in, const int* __restrict__ row_idx, bf16* __restrict__ out, int cols) {
+  pdl_wait();
+  pdl_trigger();
+  const float* src = in + (size_t)(row_idx ? row_idx[blockIdx.x] : blockIdx.x) * ld_in;
+  bf16* dst = out + (size_t)blockIdx.x * cols;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) dst[i] = f2bf(src[i]);
+}
+
+// dense bf16 rows -> rows of a strided fp32 matrix, with the activation of GemmF32::act
+__global__ void rows_bf16_to_f32_kernel(const bf16* __restrict__ in, int cols, float* __restrict__ out, int ld_out, int act) {
+  pdl_wait();
+  pdl_trigger();
+  const bf16* src = in + (size_t)blockIdx.x * cols;
+  float* dst = out + (size_t)blockIdx.x * ld_out;
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) {
+    float v = bf2f(src[i]);
+    if (act == 1) {
+      v = fmaxf(v, 0.f);
+      v = bf2f(f2bf(v * v));
+    }
+    dst[i] = v;
+  }
 }
 
 // one CTA per row: the largest logit, the lowest index among equals
@@ -191,6 +312,16 @@ __global__ void argmax_f32_kernel(const float* __restrict__ z, int* __restrict__
 
 }  // namespace
 
+cudaError_t launch_rows_f32_to_bf16(const float* in, int ld_in, const int* row_idx, bf16* out, int cols, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  return launch_k(rows_f32_to_bf16_kernel, dim3(n), dim3(256), 0, st, in, ld_in, row_idx, out, cols);
+}
+
+cudaError_t launch_rows_bf16_to_f32(const bf16* in, int cols, float* out, int ld_out, int act, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  return launch_k(rows_bf16_to_f32_kernel, dim3(n), dim3(256), 0, st, in, cols, out, ld_out, act);
+}
+
 cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, cudaStream_t st) {
   if (n_rows <= 0) return cudaSuccess;
   return launch_k(argmax_f32_kernel, dim3(n_rows), dim3(256), 0, st, z, out, vocab);
@@ -198,6 +329,16 @@ cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, c
 
 cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.batches <= 0) return cudaSuccess;
+  if (g.M <= GEMV_MAX_ROWS) {
+    if (g.w_trans && !g.grp_off && !g.row_idx && !g.bias && g.act == 0)
+      return launch_k(gemv_trans_f32_kernel, dim3((g.N + 127) / 128, g.M, g.batches), dim3(128), 0, st, g);
+    if (!g.w_trans) {
+      const bool vec = g.K % 8 == 0 && g.ldw % 8 == 0 && g.w_batch % 8 == 0 && g.lda % 4 == 0 && g.a_batch % 4 == 0 &&
+                       (reinterpret_cast<uintptr_t>(g.W) & 15) == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0;
+      const dim3 grid((g.N + 7) / 8, 1, g.batches);
+      return vec ? launch_k(gemv_f32_kernel<true>, grid, dim3(256), 0, st, g) : launch_k(gemv_f32_kernel<false>, grid, dim3(256), 0, st, g);
+    }
+  }
   dim3 grid((g.N + GT - 1) / GT, (g.M + GT - 1) / GT, g.batches);
   return launch_k(gemm_f32_kernel, grid, dim3(256), 0, st, g);
 }

@@ -271,6 +271,24 @@ class Engine:
             out[name.decode()] = (float(ms[i]), int(cnt[i]))
         return out
 
+    def profile_begin(self):
+        """bracket every launch of the following forwards with events (any family, prefill or decode)"""
+        check(self._L.qie_profile_begin(self._h))
+
+    def profile_end(self):
+        """{kernel class: (summed device ms, launches)} since profile_begin"""
+        ms = np.zeros(64, np.float32)
+        cnt = np.zeros(64, np.int32)
+        check(self._L.qie_profile_end(self._h, ms.ctypes.data, cnt.ctypes.data, 64))
+        out = {}
+        for i in range(64):
+            name = self._L.qie_kernel_kind_name(i)
+            if name is None:
+                break
+            if cnt[i]:
+                out[name.decode()] = (float(ms[i]), int(cnt[i]))
+        return out
+
     # -- persistent decode kernel ---------------------------------------------------
     def set_int(self, key, value):
         check(self._L.qie_engine_set_int(self._h, key.encode(), int(value)))

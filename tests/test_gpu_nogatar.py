@@ -290,3 +290,24 @@ def test_bfloat16_mode_is_close_and_cut_invariant(tmp_path):
     eng.close()
     assert U.rel_err(whole, want) < 5e-2
     assert U.rel_err(parts, whole) < 1e-2  # the same arithmetic per row: only tile-order rounding may differ
+
+
+def test_bfloat16_tensor_core_projections(tmp_path):
+    # sizes that fit the tcgen05 GEMM's tiles (k a multiple of 64, >= 128 output columns, > 16 rows): the projections of
+    # a long portion run on tensor cores, those of short portions and single tokens on the fp32-accumulate kernels;
+    # both must agree with the oracle and with each other within bf16 rounding
+    layers = [U.attn_layer(heads=4, dim=16, rot_dim=16, vdim=32, kv_rank=32, window=24, mlp=U.moe(experts=4, top=2, ff=64, shared_ff=128)),
+              U.mlstm_layer(heads=2, dim=16, vdim=32, mlp=None)]
+    cfg = U.make_config(layers, width=64, vocab=160)
+    w = U.random_weights(cfg, seed=71)
+    toks = _tokens(cfg, 70, 5)
+    want = _oracle_logits(cfg, w, toks)
+    eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=8)
+    whole = _whole(eng, toks)
+    s = eng.new_sequence()
+    parts = np.concatenate([eng.forward_batch([(s, toks[:40])], range(40)), eng.forward_batch([(s, toks[40:52])], range(12))] +
+                           [eng.forward_batch([(s, [t])], [0]) for t in toks[52:]])
+    eng.close()
+    assert U.rel_err(whole, want) < 5e-2
+    assert U.rel_err(parts, want) < 5e-2
+    assert U.rel_err(parts, whole) < 3e-2
