@@ -93,25 +93,31 @@ __global__ void rope_heads_kernel(const float* __restrict__ src, int ld_src, int
   for (int i = rope.dims + threadIdx.x; i < rot; i += blockDim.x) d[i] = s[i];
 }
 
-// Shared memory (floats): qa [H][D] | acc [H][rank] | tile [TK][D+1] | p [H][TK] | m [H] | l [H] | alpha [H]
+// Shared memory (floats), HP = heads of this CTA rounded up to 8:
+//   q [D][HP] | acc [HP][rank] | tile [TK][D+1] | p [TK][HP] | m [HP] | l [HP] | alpha [HP]
+// q and p are stored head-minor so that the score and the value loops read 8 heads with two 16-byte loads per cached
+// element: a thread keeps 8 heads' partial sums in registers (scores: one key x 8 heads, values: one latent
+// dimension x 8 heads), which makes both loops arithmetic-bound instead of shared-memory-bound.
 template <typename T>
 __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache c, const float* __restrict__ qa, float* __restrict__ out,
                                                                 const bf16* __restrict__ sink, float scale, int window, int H_all, int HG, int TK,
                                                                 const int* __restrict__ pos, const int* __restrict__ slot,
                                                                 const int* __restrict__ block_table, int max_pages, int n_splits,
                                                                 float* __restrict__ ws) {
-  extern __shared__ float sm[];
+  extern __shared__ float4 sm4[];
+  float* sm = reinterpret_cast<float*>(sm4);
   pdl_wait();
   pdl_trigger();
   const int D = c.rank + c.rot, DP = D + 1, R = c.rank;
   const int h0 = blockIdx.y * HG, H = min(HG, H_all - h0);  // this CTA's heads
+  const int HP = (HG + 7) & ~7, HC = HP / 8;
   float* s_q = sm;
-  float* s_acc = s_q + (size_t)H * D;
-  float* s_tile = s_acc + (size_t)H * R;
-  float* s_p = s_tile + (size_t)TK * DP;
-  float* s_m = s_p + (size_t)H * TK;
-  float* s_l = s_m + H;
-  float* s_alpha = s_l + H;
+  float* s_acc = s_q + (size_t)D * HP;
+  float* s_p = s_acc + (size_t)HP * R;
+  float* s_m = s_p + (size_t)TK * HP;
+  float* s_l = s_m + HP;
+  float* s_alpha = s_l + HP;
+  float* s_tile = s_alpha + HP;
   const int r = blockIdx.x, tid = threadIdx.x, nt = blockDim.x;
   const int p = pos[r], sl = slot[r];
   int j_lo = window > 0 ? max(0, p - window + 1) : 0, j_hi = p;
@@ -122,12 +128,17 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
     j_hi = min(p, j_lo + per * TK - 1);
   }
   const bool with_sink = sink && split == 0;
-  for (int i = tid; i < H * D; i += nt) s_q[i] = qa[((size_t)r * H_all + h0) * D + i];
-  for (int i = tid; i < H * R; i += nt) s_acc[i] = 0.f;
-  for (int h = tid; h < H; h += nt) {
+  for (int i = tid; i < HP * D; i += nt) {
+    const int d = i / HP, h = i % HP;
+    s_q[i] = h < H ? qa[((size_t)r * H_all + h0 + h) * D + d] : 0.f;
+  }
+  for (int i = tid; i < HP * R; i += nt) s_acc[i] = 0.f;
+  for (int i = tid; i < TK * HP; i += nt) s_p[i] = 0.f;
+  for (int h = tid; h < HP; h += nt) {
     // the sink enters as a key with score sink_h and no value: running maximum sink_h, running sum exp(0) = 1
-    s_m[h] = with_sink ? bf2f(sink[h0 + h]) : -INFINITY;
-    s_l[h] = with_sink ? 1.f : 0.f;
+    s_m[h] = with_sink && h < H ? bf2f(sink[h0 + h]) : -INFINITY;
+    s_l[h] = with_sink && h < H ? 1.f : 0.f;
+    s_alpha[h] = 0.f;
   }
   __syncthreads();
   for (int j0 = j_lo; j0 <= j_hi; j0 += TK) {
@@ -137,25 +148,36 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
       for (int d = tid & 31; d < D; d += 32) s_tile[jj * DP + d] = ld_elt<T>(row + d);
     }
     __syncthreads();
-    for (int i = tid; i < H * nk; i += nt) {
-      const int h = i / nk, jj = i % nk;
-      const float* q = s_q + (size_t)h * D;
+    for (int i = tid; i < HC * nk; i += nt) {  // scores of one key against 8 heads
+      const int hc = i / nk, jj = i % nk;
       const float* k = s_tile + jj * DP;
-      float s = 0.f;
-      for (int d = 0; d < D; ++d) s = fmaf(q[d], k[d], s);
-      s_p[h * TK + jj] = s * scale;
+      const float4* q4 = reinterpret_cast<const float4*>(s_q) + hc * 2;
+      float a[8] = {};
+      for (int d = 0; d < D; ++d) {
+        const float kv = k[d];
+        const float4 qa4 = q4[(size_t)d * (HP / 4)], qb4 = q4[(size_t)d * (HP / 4) + 1];
+        a[0] = fmaf(kv, qa4.x, a[0]), a[1] = fmaf(kv, qa4.y, a[1]), a[2] = fmaf(kv, qa4.z, a[2]), a[3] = fmaf(kv, qa4.w, a[3]);
+        a[4] = fmaf(kv, qb4.x, a[4]), a[5] = fmaf(kv, qb4.y, a[5]), a[6] = fmaf(kv, qb4.z, a[6]), a[7] = fmaf(kv, qb4.w, a[7]);
+      }
+      float4* dst = reinterpret_cast<float4*>(s_p + (size_t)jj * HP + hc * 8);
+      dst[0] = make_float4(a[0] * scale, a[1] * scale, a[2] * scale, a[3] * scale);
+      dst[1] = make_float4(a[4] * scale, a[5] * scale, a[6] * scale, a[7] * scale);
     }
     __syncthreads();
-    for (int h = tid >> 5; h < H; h += nt >> 5) {  // one warp per head
+    for (int h = tid >> 5; h < HP; h += nt >> 5) {  // one warp per head; heads beyond H keep probability 0
       const int lane = tid & 31;
+      if (h >= H) {
+        for (int jj = lane; jj < nk; jj += 32) s_p[jj * HP + h] = 0.f;
+        continue;
+      }
       float mx = -INFINITY;
-      for (int jj = lane; jj < nk; jj += 32) mx = fmaxf(mx, s_p[h * TK + jj]);
+      for (int jj = lane; jj < nk; jj += 32) mx = fmaxf(mx, s_p[jj * HP + h]);
       mx = warp_max(mx);
       const float m_old = s_m[h], m_new = fmaxf(m_old, mx);
       float sum = 0.f;
       for (int jj = lane; jj < nk; jj += 32) {
-        const float e = expf(s_p[h * TK + jj] - m_new);
-        s_p[h * TK + jj] = e;
+        const float e = expf(s_p[jj * HP + h] - m_new);
+        s_p[jj * HP + h] = e;
         sum += e;
       }
       sum = warp_sum(sum);
@@ -167,12 +189,20 @@ __global__ void __launch_bounds__(256) latent_attention_kernel(const LatentCache
       }
     }
     __syncthreads();
-    for (int i = tid; i < H * R; i += nt) {
-      const int h = i / R, d = i % R;
-      float a = s_acc[i] * s_alpha[h];
-      const float* pp = s_p + h * TK;
-      for (int jj = 0; jj < nk; ++jj) a = fmaf(pp[jj], s_tile[jj * DP + d], a);
-      s_acc[i] = a;
+    for (int i = tid; i < HC * R; i += nt) {  // one latent dimension for 8 heads
+      const int hc = i / R, d = i % R;
+      float a[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) a[u] = s_acc[(size_t)(hc * 8 + u) * R + d] * s_alpha[hc * 8 + u];
+      const float4* p4 = reinterpret_cast<const float4*>(s_p) + hc * 2;
+      for (int jj = 0; jj < nk; ++jj) {
+        const float cv = s_tile[jj * DP + d];
+        const float4 pa = p4[(size_t)jj * (HP / 4)], pb = p4[(size_t)jj * (HP / 4) + 1];
+        a[0] = fmaf(pa.x, cv, a[0]), a[1] = fmaf(pa.y, cv, a[1]), a[2] = fmaf(pa.z, cv, a[2]), a[3] = fmaf(pa.w, cv, a[3]);
+        a[4] = fmaf(pb.x, cv, a[4]), a[5] = fmaf(pb.y, cv, a[5]), a[6] = fmaf(pb.z, cv, a[6]), a[7] = fmaf(pb.w, cv, a[7]);
+      }
+#pragma unroll
+      for (int u = 0; u < 8; ++u) s_acc[(size_t)(hc * 8 + u) * R + d] = a[u];
     }
     __syncthreads();
   }
@@ -214,7 +244,10 @@ __global__ void latent_attention_combine_kernel(const float* __restrict__ ws, fl
   }
 }
 
-size_t attn_smem_floats(int H, int D, int R, int TK) { return (size_t)H * D + (size_t)H * R + (size_t)TK * (D + 1) + (size_t)H * TK + 3 * (size_t)H; }
+size_t attn_smem_floats(int H, int D, int R, int TK) {
+  const size_t HP = (size_t)((H + 7) & ~7);
+  return HP * D + HP * R + (size_t)TK * (D + 1) + (size_t)TK * HP + 3 * HP;
+}
 
 }  // namespace
 
@@ -240,7 +273,7 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
   // all heads of a row share the key tiles, so one CTA per row reads them once; with few rows the heads are dealt to
   // more CTAs (each reads the tiles again, from L2) until the GPU has a CTA per SM or so
   int HG = heads;
-  while (HG > 1 && (long)n * ((heads + HG - 1) / HG) < 128) HG = (HG + 1) / 2;
+  while (HG > 8 && (long)n * ((heads + HG - 1) / HG) < 128) HG = (HG + 1) / 2;  // the kernel works on heads in eights
   int TK = 128;
   if (window > 0)
     while (TK > 8 && TK / 2 >= window) TK /= 2;

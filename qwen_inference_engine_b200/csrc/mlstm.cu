@@ -44,8 +44,9 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a, int 
   const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
   float* st = a.state + (size_t)a.seg_slot[seg] * a.slot_stride;
   float* Sg = st + (size_t)h * d * vd;
-  float* ng = st + (size_t)H * d * vd + (size_t)h * d;
-  float* mg = st + (size_t)H * d * vd + (size_t)H * d + h;
+  const int nblk = (vd + 31) / 32;  // copies of n and m (mlstm_state_floats); this kernel keeps copy 0
+  float* ng = st + (size_t)H * d * vd + (size_t)h * nblk * d;
+  float* mg = st + (size_t)H * d * vd + (size_t)H * nblk * d + (size_t)h * nblk;
   float* S = s_in_smem ? s_S : Sg;
   if (s_in_smem)
     for (int i = tid; i < d * vd; i += nt) s_S[i] = Sg[i];
@@ -103,10 +104,126 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a, int 
   if (tid == 0) *mg = m;
 }
 
+
+// The same recurrence with the state in registers: a CTA owns 32 columns of one head's S for one segment, warp w
+// the rows [w * DPT, (w + 1) * DPT) of them (dim <= 4 * DPT), so a token costs DPT fused multiply-adds per thread, one
+// shared-memory reduction over the 4 warps and no global-memory latency: the next token's q, k, v and gates are
+// loaded while the current one is computed.  n and m are kept by every CTA of the head (the same arithmetic, own copy), the
+// raw outputs S^T q / denominator go to `out`; the per-head unit norm, norm weight and output gate follow in
+// mlstm_out_kernel because they need all columns of the head.
+template <int DPT>
+__global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) {
+  __shared__ float s_part[4][32];
+  __shared__ float s_dot[4];
+  pdl_wait();
+  pdl_trigger();
+  const int d = a.dim, vd = a.vdim, H = a.heads;
+  const int seg = blockIdx.x, h = blockIdx.y, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int col = blockIdx.z * 32 + lane;
+  const bool col_ok = col < vd;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  if (r0 >= r1) return;
+  float* st = a.state + (size_t)a.seg_slot[seg] * a.slot_stride;
+  float* Sg = st + (size_t)h * d * vd;
+  // every column block keeps its own copy of n and m: the CTAs of a head run independently, none reads what another writes
+  const int nblk = gridDim.z;
+  float* ng = st + (size_t)H * d * vd + ((size_t)h * nblk + blockIdx.z) * d;
+  float* mg = st + (size_t)H * d * vd + (size_t)H * nblk * d + (size_t)h * nblk + blockIdx.z;
+  const int i0 = w * DPT;
+  float S[DPT], nn[DPT];
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    const bool ok = i0 + i < d;
+    S[i] = ok && col_ok ? Sg[(size_t)(i0 + i) * vd + col] : 0.f;
+    nn[i] = ok ? ng[i0 + i] : 0.f;
+  }
+  float m = *mg;
+  const float qs = rsqrtf((float)d);
+  const int ld = a.ld;
+  // registers of the token in flight
+  float q[DPT], k[DPT], v, zi, zf;
+  auto load = [&](int r, float* qq, float* kk, float& vv, float& gi, float& gf) {
+    const float* row = a.qkvg + (size_t)r * ld;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      const bool ok = i0 + i < d;
+      qq[i] = ok ? row[h * d + i0 + i] * qs : 0.f;
+      kk[i] = ok ? row[H * d + h * d + i0 + i] : 0.f;
+    }
+    vv = col_ok ? row[2 * H * d + h * vd + col] : 0.f;
+    // the log gates of the token, off the recurrence's critical path
+    gi = a.gate_cap * tanhf(a.gates[(size_t)r * 2 * H + h] / a.gate_cap);
+    gf = log_sigmoid(a.gate_cap * tanhf(a.gates[(size_t)r * 2 * H + H + h] / a.gate_cap));
+  };
+  load(r0, q, k, v, zi, zf);
+  for (int r = r0; r < r1; ++r) {
+    float q2[DPT], k2[DPT], v2 = 0.f, zi2 = 0.f, zf2 = 0.f;
+    if (r + 1 < r1) load(r + 1, q2, k2, v2, zi2, zf2);
+    const float ig = zi, fg = zf;
+    const float m_new = fmaxf(fg + m, ig);
+    const float ea = expf(fg + m - m_new), eb = expf(ig - m_new);
+    const float bv = eb * v;
+    float acc = 0.f, dpart = 0.f;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) {
+      S[i] = fmaf(ea, S[i], k[i] * bv);
+      acc = fmaf(S[i], q[i], acc);
+      nn[i] = fmaf(ea, nn[i], eb * k[i]);
+      dpart = fmaf(nn[i], q[i], dpart);  // the same in every lane of the warp
+    }
+    s_part[w][lane] = acc;
+    if (lane == 0) s_dot[w] = dpart;
+    __syncthreads();
+    if (w == 0) {
+      const float dot = (s_dot[0] + s_dot[1]) + (s_dot[2] + s_dot[3]);
+      const float den = fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f;
+      const float o = ((s_part[0][lane] + s_part[1][lane]) + (s_part[2][lane] + s_part[3][lane])) / den;
+      if (col_ok) a.out[(size_t)r * H * vd + h * vd + col] = o;
+    }
+    __syncthreads();
+    m = m_new;
+#pragma unroll
+    for (int i = 0; i < DPT; ++i) q[i] = q2[i], k[i] = k2[i];
+    v = v2, zi = zi2, zf = zf2;
+  }
+#pragma unroll
+  for (int i = 0; i < DPT; ++i) {
+    if (i0 + i < d) {
+      if (col_ok) Sg[(size_t)(i0 + i) * vd + col] = S[i];
+      if (lane == 0) ng[i0 + i] = nn[i];
+    }
+  }
+  if (threadIdx.x == 0) *mg = m;
+}
+
+// grid (rows, heads): out = rms_unit(out) * w_norm * sigmoid(gate), in place
+__global__ void mlstm_out_kernel(const MlstmArgs a) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, h = blockIdx.y, vd = a.vdim, H = a.heads;
+  float* o = a.out + (size_t)r * H * vd + h * vd;
+  const float* g = a.qkvg + (size_t)r * a.ld + 2 * H * a.dim + H * vd + h * vd;
+  float sq = 0.f;
+  for (int j = threadIdx.x; j < vd; j += blockDim.x) sq = fmaf(o[j], o[j], sq);
+  const float rinv = 1.0f / sqrtf(block_sum_m(sq, red) / (float)vd + a.eps);
+  for (int j = threadIdx.x; j < vd; j += blockDim.x) o[j] = o[j] * rinv * bf2f(a.w_norm[h * vd + j]) / (1.0f + expf(-g[j]));
+}
+
 }  // namespace
 
 cudaError_t launch_mlstm_scan(const MlstmArgs& a, cudaStream_t st) {
   if (a.n_seg <= 0) return cudaSuccess;
+  if (a.dim <= 128) {  // state in registers, 32 columns per CTA
+    const dim3 grid(a.n_seg, a.heads, (a.vdim + 31) / 32);
+    cudaError_t r;
+    if (a.dim <= 16) r = launch_k(mlstm_scan_reg_kernel<4>, grid, dim3(128), 0, st, a);
+    else if (a.dim <= 32) r = launch_k(mlstm_scan_reg_kernel<8>, grid, dim3(128), 0, st, a);
+    else if (a.dim <= 64) r = launch_k(mlstm_scan_reg_kernel<16>, grid, dim3(128), 0, st, a);
+    else r = launch_k(mlstm_scan_reg_kernel<32>, grid, dim3(128), 0, st, a);
+    if (r != cudaSuccess) return r;
+    return launch_k(mlstm_out_kernel, dim3(a.n_rows, a.heads), dim3(128), 0, st, a);
+  }
   const size_t base = (size_t)(3 * a.dim + a.vdim + 32) * sizeof(float);
   const size_t with_s = base + (size_t)a.dim * a.vdim * sizeof(float);
   const int in_smem = with_s <= 200 * 1024 ? 1 : 0;

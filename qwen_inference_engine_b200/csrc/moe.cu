@@ -66,11 +66,17 @@ __global__ void moe_route_kernel(const float* __restrict__ z, int ldz, int exper
 }
 
 // one CTA; warp w serves experts w, w + nw, ...: an ordered compaction of the assignments that chose the expert
-__global__ void __launch_bounds__(1024) moe_group_kernel(const int* __restrict__ top_idx, int n_assign, int top, int experts, int* grp_off,
-                                                         int* __restrict__ perm_row, int* __restrict__ slot_of) {
+__global__ void __launch_bounds__(1024) moe_group_kernel(const int* top_idx, int n_assign, int top, int experts, int* grp_off,
+                                                         int* __restrict__ perm_row, int* __restrict__ slot_of, int in_smem) {
+  extern __shared__ int s_idx[];  // the assignments, when they fit (in_smem)
   pdl_wait();
   pdl_trigger();
   const int w = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (in_smem) {
+    for (int i = threadIdx.x; i < n_assign; i += blockDim.x) s_idx[i] = top_idx[i];
+    __syncthreads();
+    top_idx = s_idx;
+  }
   for (int e = w; e < experts; e += nw) {
     int cnt = 0;
     for (int i0 = 0; i0 < n_assign; i0 += 32) {
@@ -137,7 +143,14 @@ cudaError_t launch_moe_group(const int* top_idx, int n_assign, int top, int expe
   if (n_assign <= 0) return cudaSuccess;
   int threads = 32 * experts;
   threads = threads < 64 ? 64 : (threads > 1024 ? 1024 : threads);
-  return launch_k(moe_group_kernel, dim3(1), dim3(threads), 0, st, top_idx, n_assign, top, experts, grp_off, perm_row, slot_of);
+  const size_t bytes = (size_t)n_assign * sizeof(int);
+  const int in_smem = bytes <= 160 * 1024 ? 1 : 0;
+  if (in_smem && bytes > 48 * 1024) {
+    cudaError_t r = cudaFuncSetAttribute(moe_group_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(moe_group_kernel, dim3(1), dim3(threads), in_smem ? bytes : 0, st, top_idx, n_assign, top, experts, grp_off, perm_row, slot_of,
+                  in_smem);
 }
 
 cudaError_t launch_moe_combine(const float* ye, const int* slot_of, const float* top_w, int top, const float* ys, const float* z, int ldz,

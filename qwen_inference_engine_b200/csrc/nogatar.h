@@ -90,7 +90,8 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
                                     size_t ws_floats, cudaStream_t st);
 
 // ---------------------------------------------------------------- mLSTM (mlstm.cu)
-// Recurrent state of one (sequence slot, layer): per head S [dim, vdim], n [dim], m; fp32.
+// Recurrent state of one (sequence slot, layer), fp32: S [heads][dim][vdim], then n [heads][blocks][dim] and
+// m [heads][blocks] with blocks = ceil(vdim / 32) (every 32-column block of S keeps its own copy of n and m).
 struct MlstmArgs {
   const float* qkvg = nullptr;  // [n, 2*heads*dim + 2*heads*vdim]: q | k | v | output gate, head by head
   int ld = 0;
@@ -104,8 +105,11 @@ struct MlstmArgs {
   const int* seg_start = nullptr;  // [n_seg + 1] row ranges; rows of a segment are consecutive positions of one sequence
   const int* seg_slot = nullptr;   // [n_seg]
   int n_seg = 0;
+  int n_rows = 0;  // rows of all segments
 };
-inline size_t mlstm_state_floats(int heads, int dim, int vdim) { return (size_t)heads * ((size_t)dim * vdim + dim + 1); }
+inline size_t mlstm_state_floats(int heads, int dim, int vdim) {
+  return (size_t)heads * ((size_t)dim * vdim + (size_t)((vdim + 31) / 32) * (dim + 1));
+}
 cudaError_t launch_mlstm_scan(const MlstmArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------- mixture of experts (moe.cu)

@@ -602,7 +602,7 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_
       a.qkvg = m->p0, a.ld = N0, a.gates = m->p1;
       a.state = m->state + m->state_off[L.state_id], a.slot_stride = m->slot_floats;
       a.out = m->p2, a.w_norm = L.out_norm, a.heads = H, a.dim = d, a.vdim = vd, a.gate_cap = L.gate_cap, a.eps = m->eps;
-      a.seg_start = seg_start, a.seg_slot = seg_slot, a.n_seg = n_seg;
+      a.seg_start = seg_start, a.seg_slot = seg_slot, a.n_seg = n_seg, a.n_rows = n;
       NG_TRY(KK_MLSTM, launch_mlstm_scan(a, st));
       NG_TRY(KK_F32_PROJ, proj(m->p2, H * vd, L.wo, H * vd, W, m->y, W, 0, n));
     }
