@@ -7,6 +7,8 @@
 // errors are error codes rather than token 0.
 //   iengine --meta model_files/meta_data.txt --weights weights.bin --prompt 151643,785,4767 --n 128
 //   iengine --synthetic qwen2.5-0.5b --prompt 151643,785 --prompt 151643,3639 --n 32 --topk 50
+//   iengine --model DIR [--dtype float32] --prompt 5,17,3 --n 32      (a folder with config.json + model.safetensors; the
+//           family is chosen by the configuration's architecture: qie_model_families())
 //   iengine --convert model-00001-of-00002.safetensors --convert model-00002-of-00002.safetensors
 //           --meta model_files/meta_data.txt --weights weights.bin [--tie-lm-head]     (host only, then exits)
 #include <chrono>
@@ -39,18 +41,24 @@ static bool arch_config(const std::string& a, qie_config* c) {
 }
 
 int main(int argc, char** argv) {
-  std::string meta, weights, synthetic;
+  std::string meta, weights, synthetic, model_dir, dtype = "bfloat16";
   std::vector<const char*> shards;  // --convert: safetensors shards, in order (parsed_tensors(), tensor_parser.cpp:31-129)
   int tie_lm_head = 0;
   std::vector<std::vector<int32_t>> prompts;
   int n_new = 32, topk = 1, device = 0, fast = 0;
-  const int EOS = 151645;
+  int EOS = 151645;
   for (int i = 1; i < argc; ++i) {
     std::string a = argv[i];
     auto next = [&]() -> const char* { return i + 1 < argc ? argv[++i] : ""; };
     if (a == "--meta") meta = next();
     else if (a == "--weights") weights = next();
     else if (a == "--synthetic") synthetic = next();
+    else if (a == "--model") model_dir = next();
+    else if (a == "--dtype") dtype = next();
+    else if (a == "--families") {
+      printf("%s\n", qie_model_families());
+      return 0;
+    }
     else if (a == "--n") n_new = atoi(next());
     else if (a == "--topk") topk = atoi(next());
     else if (a == "--device") device = atoi(next());
@@ -77,7 +85,10 @@ int main(int argc, char** argv) {
     printf("iengine: %d tensors, %zu bytes -> %s + %s\n", n, total, weights.c_str(), meta.c_str());
     return 0;
   }
-  if (prompts.empty()) prompts.push_back({151643, 785, 4767, 315, 279, 3639, 4180, 374});  // iengine.cu:325
+  if (prompts.empty()) {
+    if (!model_dir.empty()) prompts.push_back({1, 2, 3});
+    else prompts.push_back({151643, 785, 4767, 315, 279, 3639, 4180, 374});  // iengine.cu:325
+  }
   qie_engine_opts o;
   qie_engine_opts_default(&o);
   o.device = device;
@@ -85,7 +96,11 @@ int main(int argc, char** argv) {
   o.numerics = fast ? QIE_NUMERICS_FAST : QIE_NUMERICS_REFERENCE_ORDER;
   qie_engine* e = nullptr;
   auto t0 = std::chrono::steady_clock::now();
-  if (!synthetic.empty()) {
+  o.compute_dtype = dtype == "float32" ? QIE_DTYPE_F32 : QIE_DTYPE_BF16;
+  if (!model_dir.empty()) {
+    if (qie_engine_create_from_dir(model_dir.c_str(), &o, &e)) die("engine_create_from_dir");
+    if (std::string(qie_engine_family(e)) != "qwen") EOS = -1;  // the Qwen tokenizer's end token means nothing elsewhere
+  } else if (!synthetic.empty()) {
     qie_config c;
     if (!arch_config(synthetic, &c)) {
       fprintf(stderr, "unknown --synthetic arch\n");
@@ -102,7 +117,7 @@ int main(int argc, char** argv) {
   if (topk > 1) qie_engine_set_sampling(e, topk, 1.0f, 0.7f, 1234, 1);  // qwen_main.cu:241,381-388
   qie_config c;
   qie_engine_get_config(e, &c);
-  fprintf(stderr, "model: H=%d I=%d L=%d heads=%d/%d hd=%d V=%d  (load %.2fs)\n", c.hidden, c.inter, c.layers, c.n_q, c.n_kv,
+  fprintf(stderr, "family %s  model: H=%d I=%d L=%d heads=%d/%d hd=%d V=%d  (load %.2fs)\n", qie_engine_family(e), c.hidden, c.inter, c.layers, c.n_q, c.n_kv,
           c.head_dim, c.vocab, std::chrono::duration<double>(std::chrono::steady_clock::now() - t0).count());
   const int B = (int)prompts.size();
   std::vector<int> seqs(B);
