@@ -150,6 +150,97 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32 g) {
 }
 
 
+// The same tile on tensor cores for bf16 operands (round_a): A is rounded to bf16 while it is staged, the products run
+// as mma.sync m16n8k16 with fp32 accumulators, k ascending.  8 warps: warp w owns rows (w % 4) * 16 .. + 16 and columns
+// (w / 4) * 32 .. + 32 of the 64 x 64 tile.  Rows of 32 k-elements are padded to 40 so that the 32-bit fragment loads
+// of a warp fall into 32 different banks.
+constexpr int MK = 32, MKP = 40;
+
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const uint32_t (&a)[4], const uint32_t (&b)[2]) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b[0]), "r"(b[1]));
+}
+
+__global__ void __launch_bounds__(256) gemm_bf16_mma_kernel(const GemmF32 g) {
+  __shared__ __align__(16) bf16 As[GT][MKP];
+  __shared__ __align__(16) bf16 Ws[GT][MKP];
+  __shared__ int src_row[GT];
+  pdl_wait();
+  pdl_trigger();
+  const int z = blockIdx.z;
+  int row_base = 0, Mz = g.M;
+  if (g.grp_off) {
+    row_base = g.grp_off[z];
+    Mz = g.grp_off[z + 1] - row_base;
+  }
+  const int m0 = blockIdx.y * GT, n0 = blockIdx.x * GT;
+  if (m0 >= Mz) return;
+  const int tid = threadIdx.x;
+  if (tid < GT) {
+    const int m = m0 + tid;
+    src_row[tid] = m < Mz ? (g.row_idx ? g.row_idx[row_base + m] : row_base + m) : -1;
+  }
+  __syncthreads();
+  const float* A = g.A + (size_t)z * g.a_batch;
+  const bf16* W = g.W + (size_t)z * g.w_batch;
+  const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int wm = (warp & 3) * 16, wn = (warp >> 2) * 32;
+  float acc[4][4] = {};
+  for (int k0 = 0; k0 < g.K; k0 += MK) {
+    for (int i = tid; i < GT * MK; i += 256) {
+      const int mm = i / MK, kk = i % MK;
+      const int s = src_row[mm];
+      As[mm][kk] = f2bf(s >= 0 && k0 + kk < g.K ? A[(size_t)s * g.lda + k0 + kk] : 0.f);
+    }
+    if (!g.w_trans) {
+      for (int i = tid; i < GT * MK; i += 256) {
+        const int nn = i / MK, kk = i % MK;
+        Ws[nn][kk] = n0 + nn < g.N && k0 + kk < g.K ? W[(size_t)(n0 + nn) * g.ldw + k0 + kk] : f2bf(0.f);
+      }
+    } else {
+      for (int i = tid; i < GT * MK; i += 256) {
+        const int kk = i / GT, nn = i % GT;
+        Ws[nn][kk] = n0 + nn < g.N && k0 + kk < g.K ? W[(size_t)(k0 + kk) * g.ldw + n0 + nn] : f2bf(0.f);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < MK; ks += 16) {
+      uint32_t a[4];
+      a[0] = *reinterpret_cast<const uint32_t*>(&As[wm + gq][ks + 2 * tq]);
+      a[1] = *reinterpret_cast<const uint32_t*>(&As[wm + gq + 8][ks + 2 * tq]);
+      a[2] = *reinterpret_cast<const uint32_t*>(&As[wm + gq][ks + 2 * tq + 8]);
+      a[3] = *reinterpret_cast<const uint32_t*>(&As[wm + gq + 8][ks + 2 * tq + 8]);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        uint32_t b[2];
+        b[0] = *reinterpret_cast<const uint32_t*>(&Ws[wn + j * 8 + gq][ks + 2 * tq]);
+        b[1] = *reinterpret_cast<const uint32_t*>(&Ws[wn + j * 8 + gq][ks + 2 * tq + 8]);
+        mma_bf16_16816(acc[j], a, b);
+      }
+    }
+    __syncthreads();
+  }
+  float* C = g.C + (size_t)z * g.c_batch;
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int m = m0 + wm + gq + (u >> 1) * 8, n = n0 + wn + j * 8 + 2 * tq + (u & 1);
+      if (m >= Mz || n >= g.N) continue;
+      float v = acc[j][u];
+      if (g.bias) v += bf2f(g.bias[n]);
+      if (g.act == 1) {
+        v = fmaxf(v, 0.f);
+        v = v * v;
+      }
+      if (g.round_c) v = bf2f(f2bf(v));
+      C[(size_t)(row_base + m) * g.ldc + n] = v;
+    }
+  }
+}
+
 // Few rows (decode steps, lightly loaded experts): one warp per output column streams the weight row with 16-byte
 // loads and keeps up to 8 rows of partial sums; experts without rows leave at once, so a mixture of experts reads
 // only the chosen experts' weights.  The k order per output is fixed (lane-strided, then a shuffle tree), whatever
@@ -329,7 +420,8 @@ cudaError_t launch_argmax_f32(const float* z, int* out, int n_rows, int vocab, c
 
 cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0 || g.batches <= 0) return cudaSuccess;
-  if (g.M <= GEMV_MAX_ROWS) {
+  // grouped problems (experts) split their rows, so the warp-per-column kernel pays up to far more rows in total
+  if (g.M <= (g.grp_off ? 16 * GEMV_MAX_ROWS : GEMV_MAX_ROWS)) {
     if (g.w_trans && !g.grp_off && !g.row_idx && !g.bias && g.act == 0)
       return launch_k(gemv_trans_f32_kernel, dim3((g.N + 127) / 128, g.M, g.batches), dim3(128), 0, st, g);
     if (!g.w_trans) {
@@ -340,6 +432,7 @@ cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
     }
   }
   dim3 grid((g.N + GT - 1) / GT, (g.M + GT - 1) / GT, g.batches);
+  if (g.round_a) return launch_k(gemm_bf16_mma_kernel, grid, dim3(256), 0, st, g);  // bf16 operands: tensor cores
   return launch_k(gemm_f32_kernel, grid, dim3(256), 0, st, g);
 }
 
