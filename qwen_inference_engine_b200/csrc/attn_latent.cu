@@ -246,6 +246,169 @@ __global__ void latent_attention_combine_kernel(const float* __restrict__ ws, fl
   }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// Tensor-core version for bf16 caches and many rows (prompts).  All heads of a row share the cached rows, so the
+// HEADS are the M dimension of the MMA: S [16 heads, 64 keys] = Q [16, D] K^T and O [16 heads, rank] += P [16, 64] C,
+// mma.sync m16n8k16 with fp32 accumulators.  One CTA per (row, group of <= 16 heads), 8 warps: warp w owns keys
+// 8w .. 8w+7 of a tile for the scores and the latent columns 8 (w + 8 i), i < NBW, for the values (accumulators in
+// registers across tiles, rescaled like the fp32 kernel).  Softmax state and scores are fp32; the probabilities enter
+// the second product as bf16.  Shared memory: q bf16 [16][D+8] | tile bf16 [64][D+8] | scores fp32 [16][65] |
+// probabilities bf16 [16][72] | m, l, alpha [16].
+__device__ __forceinline__ void mma_16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+               : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+constexpr int ATK = 64;  // keys per tile
+
+template <int NBW>
+__global__ void __launch_bounds__(256) latent_attention_mma_kernel(const LatentCache c, const float* __restrict__ qa, float* __restrict__ out,
+                                                                    const bf16* __restrict__ sink, float scale, int window, int H_all,
+                                                                    const int* __restrict__ pos, const int* __restrict__ slot,
+                                                                    const int* __restrict__ block_table, int max_pages) {
+  extern __shared__ uint4 smq[];
+  pdl_wait();
+  pdl_trigger();
+  const int D = c.rank + c.rot, DP = D + 8, R = c.rank, D16 = (D + 15) & ~15;
+  const int h0 = blockIdx.y * 16, H = min(16, H_all - h0);
+  bf16* s_q = reinterpret_cast<bf16*>(smq);
+  bf16* s_tile = s_q + 16 * DP;
+  float* s_s = reinterpret_cast<float*>(s_tile + ATK * DP);
+  bf16* s_pb = reinterpret_cast<bf16*>(s_s + 16 * 65);
+  float* s_m = reinterpret_cast<float*>(s_pb + 16 * 72);
+  float* s_l = s_m + 16;
+  float* s_alpha = s_l + 16;
+  const int r = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
+  const int p = pos[r], sl = slot[r];
+  const int j_lo = window > 0 ? max(0, p - window + 1) : 0;
+  for (int i = tid; i < 16 * DP; i += 256) {
+    const int h = i / DP, d = i % DP;
+    s_q[i] = f2bf(h < H && d < D ? qa[((size_t)r * H_all + h0 + h) * D + d] : 0.f);
+  }
+  if (tid < 16) {
+    const bool ws = sink && tid < H;
+    s_m[tid] = ws ? bf2f(sink[h0 + tid]) : -INFINITY;
+    s_l[tid] = ws ? 1.f : 0.f;
+    s_alpha[tid] = 0.f;
+  }
+  float o[NBW][4];
+#pragma unroll
+  for (int i = 0; i < NBW; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+  const int chunks = DP / 8;  // 16-byte pieces of a padded row; the last one is the zero padding
+  __syncthreads();
+  for (int j0 = j_lo; j0 <= p; j0 += ATK) {
+    const int nk = min(ATK, p + 1 - j0);
+    for (int jj = warp; jj < ATK; jj += 8) {  // a warp per cached row, 16-byte copies; rows past the window's end are zeros
+      uint4* dst = reinterpret_cast<uint4*>(s_tile + jj * DP);
+      if (jj < nk) {
+        const uint4* row = reinterpret_cast<const uint4*>(cache_row<bf16>(c, block_table, max_pages, sl, j0 + jj));
+        for (int ch = lane; ch < chunks; ch += 32) dst[ch] = ch < D / 8 ? row[ch] : make_uint4(0, 0, 0, 0);
+      } else {
+        for (int ch = lane; ch < chunks; ch += 32) dst[ch] = make_uint4(0, 0, 0, 0);
+      }
+    }
+    __syncthreads();
+    {  // scores of keys 8 warp .. 8 warp + 7 against the 16 heads
+      float sc[4] = {0.f, 0.f, 0.f, 0.f};
+      const bf16* krow = s_tile + (warp * 8 + gq) * DP;
+      for (int ks = 0; ks < D16; ks += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(s_q + gq * DP + ks + 2 * tq);
+        a[1] = *reinterpret_cast<const uint32_t*>(s_q + (gq + 8) * DP + ks + 2 * tq);
+        a[2] = *reinterpret_cast<const uint32_t*>(s_q + gq * DP + ks + 2 * tq + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(s_q + (gq + 8) * DP + ks + 2 * tq + 8);
+        const uint32_t b0 = *reinterpret_cast<const uint32_t*>(krow + ks + 2 * tq);
+        const uint32_t b1 = *reinterpret_cast<const uint32_t*>(krow + ks + 2 * tq + 8);
+        mma_16816(sc, a, b0, b1);
+      }
+      const int col = warp * 8 + 2 * tq;
+      s_s[gq * 65 + col] = sc[0] * scale;
+      s_s[gq * 65 + col + 1] = sc[1] * scale;
+      s_s[(gq + 8) * 65 + col] = sc[2] * scale;
+      s_s[(gq + 8) * 65 + col + 1] = sc[3] * scale;
+    }
+    __syncthreads();
+    for (int h = warp; h < 16; h += 8) {  // online softmax, one warp per head
+      float mx = -INFINITY;
+      for (int jj = lane; jj < nk; jj += 32) mx = fmaxf(mx, s_s[h * 65 + jj]);
+      mx = warp_max(mx);
+      const float m_old = s_m[h], m_new = fmaxf(m_old, mx);
+      float sum = 0.f;
+      for (int jj = lane; jj < ATK; jj += 32) {
+        const float e = jj < nk && h < H ? expf(s_s[h * 65 + jj] - m_new) : 0.f;
+        s_pb[h * 72 + jj] = f2bf(e);
+        sum += e;
+      }
+      sum = warp_sum(sum);
+      if (lane == 0) {
+        const float a = m_old == -INFINITY ? 0.f : expf(m_old - m_new);
+        s_alpha[h] = a;
+        s_l[h] = s_l[h] * a + sum;
+        s_m[h] = m_new;
+      }
+    }
+    __syncthreads();
+    {  // O = O * alpha + P C for this warp's latent columns
+      const float a_lo = s_alpha[gq], a_hi = s_alpha[gq + 8];
+#pragma unroll
+      for (int i = 0; i < NBW; ++i) o[i][0] *= a_lo, o[i][1] *= a_lo, o[i][2] *= a_hi, o[i][3] *= a_hi;
+#pragma unroll
+      for (int kk = 0; kk < ATK; kk += 16) {
+        uint32_t a[4];
+        a[0] = *reinterpret_cast<const uint32_t*>(s_pb + gq * 72 + kk + 2 * tq);
+        a[1] = *reinterpret_cast<const uint32_t*>(s_pb + (gq + 8) * 72 + kk + 2 * tq);
+        a[2] = *reinterpret_cast<const uint32_t*>(s_pb + gq * 72 + kk + 2 * tq + 8);
+        a[3] = *reinterpret_cast<const uint32_t*>(s_pb + (gq + 8) * 72 + kk + 2 * tq + 8);
+#pragma unroll
+        for (int i = 0; i < NBW; ++i) {
+          const int nb = warp + 8 * i;
+          if (nb * 8 < R) {  // warp-uniform
+            uint32_t b0, b1;
+            ldmatrix_x2_trans(b0, b1, smem_u32(s_tile + (kk + (lane & 15)) * DP + nb * 8));
+            mma_16816(o[i], a, b0, b1);
+          }
+        }
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < NBW; ++i) {
+    const int d = (warp + 8 * i) * 8 + 2 * tq;
+    if (d < R) {
+      if (gq < H) {
+        const float inv = 1.0f / s_l[gq];
+        float* dst = out + ((size_t)r * H_all + h0 + gq) * R + d;
+        dst[0] = o[i][0] * inv, dst[1] = o[i][1] * inv;
+      }
+      if (gq + 8 < H) {
+        const float inv = 1.0f / s_l[gq + 8];
+        float* dst = out + ((size_t)r * H_all + h0 + gq + 8) * R + d;
+        dst[0] = o[i][2] * inv, dst[1] = o[i][3] * inv;
+      }
+    }
+  }
+}
+
+template <int NBW>
+cudaError_t launch_attn_mma(const LatentCache& c, const float* qa, float* out, const bf16* sink, float scale, int window, int heads, const int* pos,
+                            const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st) {
+  const int DP = c.rank + c.rot + 8;
+  const size_t smem = (size_t)(16 + ATK) * DP * sizeof(bf16) + 16 * 65 * sizeof(float) + 16 * 72 * sizeof(bf16) + 48 * sizeof(float);
+  if (smem > 200 * 1024) return cudaErrorInvalidConfiguration;
+  if (smem > 48 * 1024) {
+    cudaError_t r = cudaFuncSetAttribute(latent_attention_mma_kernel<NBW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(latent_attention_mma_kernel<NBW>, dim3(n, (heads + 15) / 16), dim3(256), smem, st, c, qa, out, sink, scale, window, heads, pos, slot,
+                  block_table, max_pages);
+}
+
 size_t attn_smem_floats(int H, int D, int R, int TK) {
   const size_t HP = (size_t)((H + 7) & ~7);
   return HP * D + HP * R + (size_t)TK * (D + 1) + (size_t)TK * HP + 3 * HP;
@@ -272,6 +435,17 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
                                     size_t ws_floats, cudaStream_t st) {
   if (n <= 0) return cudaSuccess;
   const int D = c.rank + c.rot;
+  // bf16 cache rows and a prompt's worth of rows: tensor cores (QIE_ATTN_MMA=0 keeps the fp32 kernel)
+  static const bool mma_on = [] { const char* v = getenv("QIE_ATTN_MMA"); return !(v && v[0] == '0'); }();
+  if (mma_on && c.elt_bytes == 2 && n >= 64 && c.rank % 8 == 0 && c.rot % 8 == 0 && c.rank <= 512 && c.page_elems % 8 == 0 &&
+      c.layer_off % 8 == 0 && (reinterpret_cast<uintptr_t>(c.pool) & 15) == 0) {
+    cudaError_t r = cudaErrorInvalidConfiguration;
+    if (c.rank <= 64) r = launch_attn_mma<1>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
+    else if (c.rank <= 128) r = launch_attn_mma<2>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
+    else if (c.rank <= 256) r = launch_attn_mma<4>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
+    else r = launch_attn_mma<8>(c, qa, out, sink, scale, window, heads, pos, slot, block_table, max_pages, n, st);
+    if (r != cudaErrorInvalidConfiguration) return r;  // too large for its shared memory: the fp32 kernel below
+  }
   // all heads of a row share the key tiles, so one CTA per row reads them once; with few rows the heads are dealt to
   // more CTAs (each reads the tiles again, from L2) until the GPU has a CTA per SM or so
   int HG = heads;

@@ -241,6 +241,41 @@ __global__ void __launch_bounds__(256) gemm_bf16_mma_kernel(const GemmF32 g) {
   }
 }
 
+// Few output columns, many rows (router logits, gate pre-activations): a warp per row reads the row once and keeps all
+// columns' partial sums; k lane-strided, then a shuffle tree -- the order per output is fixed.
+constexpr int SKINNY_N = 32;
+__global__ void __launch_bounds__(256) gemm_skinny_f32_kernel(const GemmF32 g) {
+  pdl_wait();
+  pdl_trigger();
+  const int m = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+  if (m >= g.M) return;
+  const float* a = g.A + (size_t)m * g.lda;
+  float acc[SKINNY_N] = {};
+  for (int k = lane; k < g.K; k += 32) {
+    float av = a[k];
+    if (g.round_a) av = bf2f(f2bf(av));
+#pragma unroll
+    for (int n = 0; n < SKINNY_N; ++n)
+      if (n < g.N) acc[n] = fmaf(av, bf2f(g.W[(size_t)n * g.ldw + k]), acc[n]);
+  }
+#pragma unroll
+  for (int n = 0; n < SKINNY_N; ++n) {
+    if (n < g.N) {
+      float v = acc[n];
+      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+      if (lane == 0) {
+        if (g.bias) v += bf2f(g.bias[n]);
+        if (g.act == 1) {
+          v = fmaxf(v, 0.f);
+          v = v * v;
+        }
+        if (g.round_c) v = bf2f(f2bf(v));
+        g.C[(size_t)m * g.ldc + n] = v;
+      }
+    }
+  }
+}
+
 // Few rows (decode steps, lightly loaded experts): one warp per output column streams the weight row with 16-byte
 // loads and keeps up to 8 rows of partial sums; experts without rows leave at once, so a mixture of experts reads
 // only the chosen experts' weights.  The k order per output is fixed (lane-strided, then a shuffle tree), whatever
@@ -431,6 +466,8 @@ cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
       return vec ? launch_k(gemv_f32_kernel<true>, grid, dim3(256), 0, st, g) : launch_k(gemv_f32_kernel<false>, grid, dim3(256), 0, st, g);
     }
   }
+  if (g.N <= SKINNY_N && !g.w_trans && !g.grp_off && !g.row_idx && g.batches == 1)
+    return launch_k(gemm_skinny_f32_kernel, dim3((g.M + 7) / 8), dim3(256), 0, st, g);
   dim3 grid((g.N + GT - 1) / GT, (g.M + GT - 1) / GT, g.batches);
   if (g.round_a) return launch_k(gemm_bf16_mma_kernel, grid, dim3(256), 0, st, g);  // bf16 operands: tensor cores
   return launch_k(gemm_f32_kernel, grid, dim3(256), 0, st, g);
