@@ -107,19 +107,24 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a, int 
 
 // The same recurrence with the state in registers: a CTA owns 32 columns of one head's S for one segment, warp w
 // the rows [w * DPT, (w + 1) * DPT) of them (dim <= 4 * DPT), so a token costs DPT fused multiply-adds per thread, one
-// shared-memory reduction over the 4 warps and no global-memory latency: the next token's q, k, v and gates are
-// loaded while the current one is computed.  n and m are kept by every CTA of the head (the same arithmetic, own copy), the
+// shared-memory reduction over the 4 warps (one barrier) and no global-memory latency: the inputs of the next 16
+// tokens (q, k, this CTA's v columns, the log gates) are fetched into registers while the current 16 are computed from
+// shared memory.  n and m are kept by every CTA of the head (the same arithmetic, own copy), the
 // raw outputs S^T q / denominator go to `out`; the per-head unit norm, norm weight and output gate follow in
 // mlstm_out_kernel because they need all columns of the head.
 template <int DPT>
 __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) {
-  __shared__ float s_part[4][32];
-  __shared__ float s_dot[4];
+  constexpr int CH = 16;  // tokens staged per chunk
+  // [2][CH][stride]: q (scaled, zero-padded to 4 * DPT) | k (same) | v of this CTA's 32 columns | log input gate | log forget gate
+  extern __shared__ float4 s_in4[];
+  float* s_in = reinterpret_cast<float*>(s_in4);
+  __shared__ float s_part[2][4][32];
+  __shared__ float s_dot[2][4];
   pdl_wait();
   pdl_trigger();
   const int d = a.dim, vd = a.vdim, H = a.heads;
-  const int seg = blockIdx.x, h = blockIdx.y, w = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int col = blockIdx.z * 32 + lane;
+  const int seg = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, w = tid >> 5, lane = tid & 31;
+  const int col0 = blockIdx.z * 32, col = col0 + lane;
   const bool col_ok = col < vd;
   const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
   if (r0 >= r1) return;
@@ -140,51 +145,83 @@ __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) 
   float m = *mg;
   const float qs = rsqrtf((float)d);
   const int ld = a.ld;
-  // registers of the token in flight
-  float q[DPT], k[DPT], v, zi, zf;
-  auto load = [&](int r, float* qq, float* kk, float& vv, float& gi, float& gf) {
-    const float* row = a.qkvg + (size_t)r * ld;
+  constexpr int DQ = 4 * DPT, stride = 2 * DQ + 36;  // a multiple of 4 floats: rows are read with 16-byte loads
+  constexpr int PER = (stride + 127) / 128;         // staged elements of one token per thread
+  float stage[CH][PER];
+  // the inputs of chunk c: global -> registers (in flight while the previous chunk is computed) -> shared memory
+  auto fetch = [&](int c) {
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-      const bool ok = i0 + i < d;
-      qq[i] = ok ? row[h * d + i0 + i] * qs : 0.f;
-      kk[i] = ok ? row[H * d + h * d + i0 + i] : 0.f;
+    for (int t = 0; t < CH; ++t) {
+      const int r = r0 + c * CH + t;
+      const float* row = a.qkvg + (size_t)min(r, r1 - 1) * ld;
+#pragma unroll
+      for (int u = 0; u < PER; ++u) {
+        const int j = tid + u * 128;
+        float v = 0.f;
+        if (j < DQ) v = j < d ? row[h * d + j] * qs : 0.f;
+        else if (j < 2 * DQ) v = j - DQ < d ? row[H * d + h * d + (j - DQ)] : 0.f;
+        else if (j < 2 * DQ + 32) v = col0 + j - 2 * DQ < vd ? row[2 * H * d + h * vd + col0 + j - 2 * DQ] : 0.f;
+        else if (j == 2 * DQ + 32) v = a.gates[(size_t)min(r, r1 - 1) * 2 * H + h];       // log gates, transformed by mlstm_gates_kernel
+        else if (j == 2 * DQ + 33) v = a.gates[(size_t)min(r, r1 - 1) * 2 * H + H + h];
+        stage[t][u] = v;
+      }
     }
-    vv = col_ok ? row[2 * H * d + h * vd + col] : 0.f;
-    // the log gates of the token, off the recurrence's critical path
-    gi = a.gate_cap * tanhf(a.gates[(size_t)r * 2 * H + h] / a.gate_cap);
-    gf = log_sigmoid(a.gate_cap * tanhf(a.gates[(size_t)r * 2 * H + H + h] / a.gate_cap));
   };
-  load(r0, q, k, v, zi, zf);
-  for (int r = r0; r < r1; ++r) {
-    float q2[DPT], k2[DPT], v2 = 0.f, zi2 = 0.f, zf2 = 0.f;
-    if (r + 1 < r1) load(r + 1, q2, k2, v2, zi2, zf2);
-    const float ig = zi, fg = zf;
-    const float m_new = fmaxf(fg + m, ig);
-    const float ea = expf(fg + m - m_new), eb = expf(ig - m_new);
-    const float bv = eb * v;
-    float acc = 0.f, dpart = 0.f;
+  auto put = [&](int c) {
+    float* dst = s_in + (size_t)(c & 1) * CH * stride;
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) {
-      S[i] = fmaf(ea, S[i], k[i] * bv);
-      acc = fmaf(S[i], q[i], acc);
-      nn[i] = fmaf(ea, nn[i], eb * k[i]);
-      dpart = fmaf(nn[i], q[i], dpart);  // the same in every lane of the warp
-    }
-    s_part[w][lane] = acc;
-    if (lane == 0) s_dot[w] = dpart;
-    __syncthreads();
-    if (w == 0) {
-      const float dot = (s_dot[0] + s_dot[1]) + (s_dot[2] + s_dot[3]);
-      const float den = fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f;
-      const float o = ((s_part[0][lane] + s_part[1][lane]) + (s_part[2][lane] + s_part[3][lane])) / den;
-      if (col_ok) a.out[(size_t)r * H * vd + h * vd + col] = o;
-    }
-    __syncthreads();
-    m = m_new;
+    for (int t = 0; t < CH; ++t)
 #pragma unroll
-    for (int i = 0; i < DPT; ++i) q[i] = q2[i], k[i] = k2[i];
-    v = v2, zi = zi2, zf = zf2;
+      for (int u = 0; u < PER; ++u) {
+        const int j = tid + u * 128;
+        if (j < stride) dst[t * stride + j] = stage[t][u];
+      }
+  };
+  const int n_chunks = (r1 - r0 + CH - 1) / CH;
+  fetch(0);
+  put(0);
+  __syncthreads();
+  int par = 0;
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + 1 < n_chunks) fetch(c + 1);
+    const float* in = s_in + (size_t)(c & 1) * CH * stride;
+    const int nt = min(CH, r1 - r0 - c * CH);
+    for (int t = 0; t < nt; ++t) {
+      const float* tk = in + t * stride;
+      const float ig = tk[2 * DQ + 32], fg = tk[2 * DQ + 33], v = tk[2 * DQ + lane];
+      const float4* q4 = reinterpret_cast<const float4*>(tk + i0);
+      const float4* k4 = reinterpret_cast<const float4*>(tk + DQ + i0);
+      const float m_new = fmaxf(fg + m, ig);
+      const float ea = expf(fg + m - m_new), eb = expf(ig - m_new);
+      const float bv = eb * v;
+      float acc = 0.f, dpart = 0.f;
+#pragma unroll
+      for (int i4 = 0; i4 < DPT / 4; ++i4) {
+        const float4 qv = q4[i4], kv = k4[i4];
+        const float q[4] = {qv.x, qv.y, qv.z, qv.w}, k[4] = {kv.x, kv.y, kv.z, kv.w};
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+          const int i = i4 * 4 + u;
+          S[i] = fmaf(ea, S[i], k[u] * bv);
+          acc = fmaf(S[i], q[u], acc);
+          nn[i] = fmaf(ea, nn[i], eb * k[u]);
+          dpart = fmaf(nn[i], q[u], dpart);  // the same in every lane of the warp
+        }
+      }
+      s_part[par][w][lane] = acc;
+      if (lane == 0) s_dot[par][w] = dpart;
+      __syncthreads();  // one barrier per token: the partial sums alternate between two buffers
+      if (w == 0) {
+        const float dot = (s_dot[par][0] + s_dot[par][1]) + (s_dot[par][2] + s_dot[par][3]);
+        const float den = fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f;
+        const float o = ((s_part[par][0][lane] + s_part[par][1][lane]) + (s_part[par][2][lane] + s_part[par][3][lane])) / den;
+        if (col_ok) a.out[(size_t)(r0 + c * CH + t) * H * vd + h * vd + col] = o;
+      }
+      par ^= 1;
+      m = m_new;
+    }
+    if (c + 1 < n_chunks) put(c + 1);
+    __syncthreads();
   }
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
@@ -193,7 +230,18 @@ __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) 
       if (lane == 0) ng[i0 + i] = nn[i];
     }
   }
-  if (threadIdx.x == 0) *mg = m;
+  if (tid == 0) *mg = m;
+}
+
+// pre-activations -> log gates, in place, for all rows at once (tanh, log-sigmoid and exp cost a few hundred instructions
+// per value: inside the scan they were the critical path of every token)
+__global__ void mlstm_gates_kernel(float* gates, int n, int H, float cap) {
+  pdl_wait();
+  pdl_trigger();
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n * 2 * H) return;
+  const float z = cap * tanhf(gates[i] / cap);
+  gates[i] = (i % (2 * H)) < H ? z : log_sigmoid(z);
 }
 
 // grid (rows, heads): out = rms_unit(out) * w_norm * sigmoid(gate), in place
@@ -216,11 +264,15 @@ cudaError_t launch_mlstm_scan(const MlstmArgs& a, cudaStream_t st) {
   if (a.n_seg <= 0) return cudaSuccess;
   if (a.dim <= 128) {  // state in registers, 32 columns per CTA
     const dim3 grid(a.n_seg, a.heads, (a.vdim + 31) / 32);
+    cudaError_t rg = launch_k(mlstm_gates_kernel, dim3((a.n_rows * 2 * a.heads + 255) / 256), dim3(256), 0, st, a.gates, a.n_rows, a.heads, a.gate_cap);
+    if (rg != cudaSuccess) return rg;
+    const int dpt = a.dim <= 16 ? 4 : a.dim <= 32 ? 8 : a.dim <= 64 ? 16 : 32;
+    const size_t smem = (size_t)2 * 16 * (8 * dpt + 36) * sizeof(float);  // two chunks of 16 staged tokens (<= 37 KB)
     cudaError_t r;
-    if (a.dim <= 16) r = launch_k(mlstm_scan_reg_kernel<4>, grid, dim3(128), 0, st, a);
-    else if (a.dim <= 32) r = launch_k(mlstm_scan_reg_kernel<8>, grid, dim3(128), 0, st, a);
-    else if (a.dim <= 64) r = launch_k(mlstm_scan_reg_kernel<16>, grid, dim3(128), 0, st, a);
-    else r = launch_k(mlstm_scan_reg_kernel<32>, grid, dim3(128), 0, st, a);
+    if (a.dim <= 16) r = launch_k(mlstm_scan_reg_kernel<4>, grid, dim3(128), smem, st, a);
+    else if (a.dim <= 32) r = launch_k(mlstm_scan_reg_kernel<8>, grid, dim3(128), smem, st, a);
+    else if (a.dim <= 64) r = launch_k(mlstm_scan_reg_kernel<16>, grid, dim3(128), smem, st, a);
+    else r = launch_k(mlstm_scan_reg_kernel<32>, grid, dim3(128), smem, st, a);
     if (r != cudaSuccess) return r;
     return launch_k(mlstm_out_kernel, dim3(a.n_rows, a.heads), dim3(128), 0, st, a);
   }

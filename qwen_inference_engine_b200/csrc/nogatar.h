@@ -95,7 +95,7 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
 struct MlstmArgs {
   const float* qkvg = nullptr;  // [n, 2*heads*dim + 2*heads*vdim]: q | k | v | output gate, head by head
   int ld = 0;
-  const float* gates = nullptr;  // [n, 2*heads]: input-gate and forget-gate pre-activations (bias added)
+  float* gates = nullptr;  // [n, 2*heads]: input-gate and forget-gate pre-activations (bias added); overwritten by the log gates
   float* state = nullptr;        // slot s at state + s * slot_stride
   size_t slot_stride = 0;
   float* out = nullptr;  // [n, heads*vdim]
