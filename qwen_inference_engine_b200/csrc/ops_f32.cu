@@ -241,36 +241,72 @@ __global__ void __launch_bounds__(256) gemm_bf16_mma_kernel(const GemmF32 g) {
   }
 }
 
-// Few output columns, many rows (router logits, gate pre-activations): a warp per row reads the row once and keeps all
-// columns' partial sums; k lane-strided, then a shuffle tree -- the order per output is fixed.
-constexpr int SKINNY_N = 32;
+// Few output columns, many rows (router logits, gate pre-activations): the weights go to shared memory once per CTA,
+// transposed to [k][NP] fp32 (NP = columns rounded up to 4), a warp per row reads its row once (k lane-strided) and
+// keeps all columns' partial sums, fed by 16-byte shared-memory loads; then a shuffle tree.  The k order per output
+// is fixed.  K is walked in chunks of SKINNY_KC.
+constexpr int SKINNY_N = 64;  // widest case; instantiated for <= 32 columns (16 rows per CTA, k chunks of 1024) and <= 64 (8 rows, 512)
+template <int SKINNY_N, int SKINNY_ROWS, int SKINNY_KC>
 __global__ void __launch_bounds__(256) gemm_skinny_f32_kernel(const GemmF32 g) {
+  extern __shared__ float4 s_w4[];
+  float* s_w = reinterpret_cast<float*>(s_w4);
   pdl_wait();
   pdl_trigger();
-  const int m = blockIdx.x * 8 + (threadIdx.x >> 5), lane = threadIdx.x & 31;
-  if (m >= g.M) return;
-  const float* a = g.A + (size_t)m * g.lda;
-  float acc[SKINNY_N] = {};
-  for (int k = lane; k < g.K; k += 32) {
-    float av = a[k];
-    if (g.round_a) av = bf2f(f2bf(av));
+  const int NP = (g.N + 3) & ~3, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m_base = blockIdx.x * SKINNY_ROWS;
+  float acc[SKINNY_ROWS / 8][SKINNY_N];
 #pragma unroll
-    for (int n = 0; n < SKINNY_N; ++n)
-      if (n < g.N) acc[n] = fmaf(av, bf2f(g.W[(size_t)n * g.ldw + k]), acc[n]);
+  for (int r = 0; r < SKINNY_ROWS / 8; ++r)
+#pragma unroll
+    for (int n = 0; n < SKINNY_N; ++n) acc[r][n] = 0.f;
+  for (int k0 = 0; k0 < g.K; k0 += SKINNY_KC) {
+    const int kc = min(SKINNY_KC, g.K - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < NP * kc; i += 256) {
+      const int n = i / kc, k = i % kc;  // k fastest: coalesced weight reads
+      s_w[k * NP + n] = n < g.N ? bf2f(g.W[(size_t)n * g.ldw + k0 + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int r = 0; r < SKINNY_ROWS / 8; ++r) {
+      const int m = m_base + warp + 8 * r;
+      if (m >= g.M) continue;
+      const float* a = g.A + (size_t)m * g.lda + k0;
+      for (int k = lane; k < kc; k += 32) {
+        float av = a[k];
+        if (g.round_a) av = bf2f(f2bf(av));
+        const float4* w4 = reinterpret_cast<const float4*>(s_w + (size_t)k * NP);
+#pragma unroll
+        for (int j = 0; j < SKINNY_N / 4; ++j) {
+          if (j * 4 < NP) {
+            const float4 wv = w4[j];
+            acc[r][4 * j] = fmaf(av, wv.x, acc[r][4 * j]);
+            acc[r][4 * j + 1] = fmaf(av, wv.y, acc[r][4 * j + 1]);
+            acc[r][4 * j + 2] = fmaf(av, wv.z, acc[r][4 * j + 2]);
+            acc[r][4 * j + 3] = fmaf(av, wv.w, acc[r][4 * j + 3]);
+          }
+        }
+      }
+    }
   }
 #pragma unroll
-  for (int n = 0; n < SKINNY_N; ++n) {
-    if (n < g.N) {
-      float v = acc[n];
-      for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-      if (lane == 0) {
-        if (g.bias) v += bf2f(g.bias[n]);
-        if (g.act == 1) {
-          v = fmaxf(v, 0.f);
-          v = v * v;
+  for (int r = 0; r < SKINNY_ROWS / 8; ++r) {
+    const int m = m_base + warp + 8 * r;
+    if (m >= g.M) continue;
+#pragma unroll
+    for (int n = 0; n < SKINNY_N; ++n) {
+      if (n < g.N) {
+        float v = acc[r][n];
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0) {
+          if (g.bias) v += bf2f(g.bias[n]);
+          if (g.act == 1) {
+            v = fmaxf(v, 0.f);
+            v = v * v;
+          }
+          if (g.round_c) v = bf2f(f2bf(v));
+          g.C[(size_t)m * g.ldc + n] = v;
         }
-        if (g.round_c) v = bf2f(f2bf(v));
-        g.C[(size_t)m * g.ldc + n] = v;
       }
     }
   }
@@ -466,8 +502,16 @@ cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st) {
       return vec ? launch_k(gemv_f32_kernel<true>, grid, dim3(256), 0, st, g) : launch_k(gemv_f32_kernel<false>, grid, dim3(256), 0, st, g);
     }
   }
-  if (g.N <= SKINNY_N && !g.w_trans && !g.grp_off && !g.row_idx && g.batches == 1)
-    return launch_k(gemm_skinny_f32_kernel, dim3((g.M + 7) / 8), dim3(256), 0, st, g);
+  if (g.N <= SKINNY_N && !g.w_trans && !g.grp_off && !g.row_idx && g.batches == 1) {
+    const bool wide = g.N > 32;
+    const size_t smem = (size_t)((g.N + 3) & ~3) * (wide ? 512 : 1024) * sizeof(float);  // <= 128 KB
+    auto* kern = wide ? gemm_skinny_f32_kernel<64, 8, 512> : gemm_skinny_f32_kernel<32, 16, 1024>;
+    if (smem > 48 * 1024) {
+      cudaError_t r = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 128 * 1024);
+      if (r != cudaSuccess) return r;
+    }
+    return launch_k(kern, dim3((g.M + (wide ? 8 : 16) - 1) / (wide ? 8 : 16)), dim3(256), smem, st, g);
+  }
   dim3 grid((g.N + GT - 1) / GT, (g.M + GT - 1) / GT, g.batches);
   if (g.round_a) return launch_k(gemm_bf16_mma_kernel, grid, dim3(256), 0, st, g);  // bf16 operands: tensor cores
   return launch_k(gemm_f32_kernel, grid, dim3(256), 0, st, g);

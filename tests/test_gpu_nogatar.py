@@ -319,3 +319,22 @@ def test_bfloat16_tensor_core_projections(tmp_path):
     for got, ref in ((whole, want), (parts, want), (parts, whole)):
         err = _row_errors(got, ref)
         assert np.median(err) < 2e-2 and np.quantile(err, 0.8) < 6e-2 and err.max() < 0.5
+
+
+def test_bfloat16_tensor_core_attention_odd_shapes(tmp_path):
+    # 5 heads (padded to the 16 rows of the MMA), latent 24 + rotated 16 = 40 (zero-padded to 48 in the k loop), rank 24
+    # = 3 column blocks for 8 warps, a window that ends inside a 64-key tile, a prompt of more than 64 rows
+    layers = [U.attn_layer(heads=5, dim=8, rot_dim=16, vdim=8, kv_rank=24, window=70, mlp=None),
+              U.attn_layer(heads=18, dim=4, rot_dim=8, vdim=4, kv_rank=8, window=0, scaling=False, mlp=None)]
+    cfg = U.make_config(layers, width=40, vocab=90)
+    w = U.random_weights(cfg, seed=81)
+    toks = _tokens(cfg, 150, 8)
+    want = _oracle_logits(cfg, w, toks)
+    eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=12)
+    whole = _whole(eng, toks)
+    s = eng.new_sequence()
+    parts = np.concatenate([eng.forward_batch([(s, toks[:100])], range(100))] + [eng.forward_batch([(s, [t])], [0]) for t in toks[100:]])
+    eng.close()
+    for got in (whole, parts):
+        err = _row_errors(got, want)
+        assert np.median(err) < 2e-2 and err.max() < 0.15
