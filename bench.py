@@ -418,10 +418,10 @@ def nogatar_config(z, vocab=32000):
     moe = {"kind": "moe", "expert": {"ff": z["ff"]}, "router": {"experts": z["experts"], "top": z["top"]}, "shared": {"ff": z["sff"]}}
     att = {"type": "latent_attention", "mlp": moe,
            "mixer": {"dim": z["dim"], "heads": z["heads"], "kv_rank": z["rank"], "mask": {"size": z["window"]}, "rot_dim": z["rot"],
-                     "rot": {"base": 500000.0, "dims": z["rot"], "scaling": {"factor": 4.0, "fast": 32.0, "original": 1024, "slow": 1.0}},
+                     "rot": {"base": 10000.0, "dims": z["rot"], "scaling": {"factor": 8.0, "fast": 32.0, "original": 2048, "slow": 1.0}},
                      "scale": (z["dim"] + z["rot"]) ** -0.5, "vdim": z["vdim"]}}
-    rec = {"type": "mlstm", "mlp": moe, "mixer": {"dim": z["md"], "gate_cap": 15.0, "heads": z["mh"], "vdim": z["mvd"]}}
-    return {"architecture": "Nogatar", "embedding": {"scale": 1.0}, "layers": [att, att, rec, att], "logit_softcap": 30.0,
+    rec = {"type": "mlstm", "mlp": moe, "mixer": {"dim": z["md"], "gate_cap": 10.0, "heads": z["mh"], "vdim": z["mvd"]}}
+    return {"architecture": "Nogatar", "embedding": {"scale": 1.0}, "layers": [att, att, rec, att], "logit_softcap": 50.0,
             "norm": {"eps": 1e-6}, "residual_mult": 0.5, "vocab": vocab, "width": z["width"]}
 
 

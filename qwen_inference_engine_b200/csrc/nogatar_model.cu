@@ -92,7 +92,8 @@ std::string parse_config(const JsonValue& root, NgModel* m) {
     } else if (type->str == "mlstm") {
       L.type = 1;
       L.state_id = n_state++;
-      L.gate_cap = (float)(mx->have("gate_cap") ? mx->have("gate_cap")->number_or(15.0) : 15.0);
+      NEED(mx->have("gate_cap") && mx->have("gate_cap")->is_number() && mx->have("gate_cap")->num > 0, "config.json: mlstm without gate_cap");
+      L.gate_cap = (float)mx->have("gate_cap")->num;
     } else {
       return "config.json: unknown layer type '" + type->str + "'";
     }
