@@ -450,6 +450,8 @@ cudaError_t launch_latent_attention(const LatentCache& c, const float* qa, float
   // more CTAs (each reads the tiles again, from L2) until the GPU has a CTA per SM or so
   int HG = heads;
   while (HG > 8 && (long)n * ((heads + HG - 1) / HG) < 128) HG = (HG + 1) / 2;  // the kernel works on heads in eights
+  // many or wide heads: the q / accumulator part of a CTA must leave room for a key tile
+  while (HG > 8 && attn_smem_floats(HG, D, c.rank, 8) > 200 * 1024 / sizeof(float)) HG = (HG + 1) / 2;
   int TK = 128;
   if (window > 0)
     while (TK > 8 && TK / 2 >= window) TK /= 2;

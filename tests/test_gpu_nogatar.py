@@ -65,9 +65,11 @@ MIXED = [U.attn_layer(mlp=U.moe()), U.mlstm_layer(mlp=U.moe(experts=4, top=1, ff
     U.attn_layer(heads=4, dim=4, rot_dim=2, vdim=4, kv_rank=4, window=1, mlp=None),  # a window of the token itself
     U.mlstm_layer(mlp=None),
     U.mlstm_layer(heads=1, dim=3, vdim=2, gate_cap=2.0, mlp=None),
+    U.mlstm_layer(heads=1, dim=132, vdim=35, mlp=None),                     # more rows than the register kernel holds
+    U.attn_layer(heads=70, dim=2, rot_dim=2, vdim=2, kv_rank=400, window=9, mlp=None),  # heads x rank beyond one CTA's shared memory
     U.attn_layer(mlp=U.moe(experts=6, top=2, ff=8, shared_ff=5)),
     U.mlstm_layer(mlp=U.moe(experts=2, top=1, ff=5, shared_ff=0)),
-], ids=["attn", "attn_full_partrot", "attn_window1", "mlstm", "mlstm_1head", "attn_moe", "mlstm_moe_noshared"])
+], ids=["attn", "attn_full_partrot", "attn_window1", "mlstm", "mlstm_1head", "mlstm_wide", "attn_many_heads", "attn_moe", "mlstm_moe_noshared"])
 def test_single_layer_matches_oracle(tmp_path, layer):
     cfg = U.make_config([layer], width=20, vocab=37)
     w = U.random_weights(cfg, seed=3)
