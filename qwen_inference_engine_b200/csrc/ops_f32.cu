@@ -187,13 +187,34 @@ __global__ void __launch_bounds__(256) gemm_bf16_mma_kernel(const GemmF32 g) {
   const int warp = tid >> 5, lane = tid & 31, gq = lane >> 2, tq = lane & 3;
   const int wm = (warp & 3) * 16, wn = (warp >> 2) * 32;
   float acc[4][4] = {};
+  // staging: a thread moves 8 consecutive k of one row with 16-byte loads when the operands allow it
+  const bool a_vec = g.lda % 4 == 0 && g.a_batch % 4 == 0 && (reinterpret_cast<uintptr_t>(g.A) & 15) == 0;
+  const bool w_vec = !g.w_trans && g.ldw % 8 == 0 && g.w_batch % 8 == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0;
+  const int srow = tid >> 2, sk = (tid & 3) * 8;
   for (int k0 = 0; k0 < g.K; k0 += MK) {
-    for (int i = tid; i < GT * MK; i += 256) {
-      const int mm = i / MK, kk = i % MK;
-      const int s = src_row[mm];
-      As[mm][kk] = f2bf(s >= 0 && k0 + kk < g.K ? A[(size_t)s * g.lda + k0 + kk] : 0.f);
+    const bool full = k0 + MK <= g.K;
+    if (a_vec && full) {
+      const int s = src_row[srow];
+      uint4 pk = make_uint4(0, 0, 0, 0);
+      if (s >= 0) {
+        const float4 v0 = *reinterpret_cast<const float4*>(A + (size_t)s * g.lda + k0 + sk);
+        const float4 v1 = *reinterpret_cast<const float4*>(A + (size_t)s * g.lda + k0 + sk + 4);
+        pk.x = pack2(f2bf(v0.x), f2bf(v0.y)), pk.y = pack2(f2bf(v0.z), f2bf(v0.w));
+        pk.z = pack2(f2bf(v1.x), f2bf(v1.y)), pk.w = pack2(f2bf(v1.z), f2bf(v1.w));
+      }
+      *reinterpret_cast<uint4*>(&As[srow][sk]) = pk;
+    } else {
+      for (int i = tid; i < GT * MK; i += 256) {
+        const int mm = i / MK, kk = i % MK;
+        const int s = src_row[mm];
+        As[mm][kk] = f2bf(s >= 0 && k0 + kk < g.K ? A[(size_t)s * g.lda + k0 + kk] : 0.f);
+      }
     }
-    if (!g.w_trans) {
+    if (w_vec && full) {
+      uint4 pk = make_uint4(0, 0, 0, 0);
+      if (n0 + srow < g.N) pk = *reinterpret_cast<const uint4*>(W + (size_t)(n0 + srow) * g.ldw + k0 + sk);
+      *reinterpret_cast<uint4*>(&Ws[srow][sk]) = pk;
+    } else if (!g.w_trans) {
       for (int i = tid; i < GT * MK; i += 256) {
         const int nn = i / MK, kk = i % MK;
         Ws[nn][kk] = n0 + nn < g.N && k0 + kk < g.K ? W[(size_t)(n0 + nn) * g.ldw + k0 + kk] : f2bf(0.f);
