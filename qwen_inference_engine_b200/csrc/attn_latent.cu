@@ -52,7 +52,7 @@ __device__ __forceinline__ T* cache_row(const LatentCache& c, const int* block_t
 template <typename T>
 __global__ void latent_store_kernel(const LatentCache c, const float* __restrict__ dkv, int ld, const bf16* __restrict__ w_norm, float eps,
                                     const RopeTable rope, const int* __restrict__ pos, const int* __restrict__ slot,
-                                    const int* __restrict__ block_table, int max_pages) {
+                                    const int* __restrict__ block_table, int max_pages, const QueryRope qr) {
   __shared__ float red[4];
   pdl_wait();
   pdl_trigger();
@@ -75,6 +75,23 @@ __global__ void latent_store_kernel(const LatentCache c, const float* __restrict
     st_elt<T>(dst + c.rank + 2 * i + 1, v * cs + u * sn);
   }
   for (int i = rope.dims + threadIdx.x; i < c.rot; i += blockDim.x) st_elt<T>(dst + c.rank + i, src[c.rank + i]);
+  // the same rotation on the rotated part of every query head of the row (saves a launch per layer)
+  if (qr.src) {
+    for (int i = threadIdx.x; i < qr.heads * half; i += blockDim.x) {
+      const int h = i / half, j = i % half;
+      const float* qs = qr.src + (size_t)r * qr.ld_src + (size_t)h * qr.hs_src;
+      float* qd = qr.dst + (size_t)r * qr.ld_dst + (size_t)h * qr.hs_dst;
+      const float cs = rope.cos_t[(size_t)p * half + j], sn = rope.sin_t[(size_t)p * half + j];
+      const float u = qs[2 * j], v = qs[2 * j + 1];
+      qd[2 * j] = u * cs - v * sn;
+      qd[2 * j + 1] = v * cs + u * sn;
+    }
+    const int rest = c.rot - rope.dims;
+    for (int i = threadIdx.x; i < qr.heads * rest; i += blockDim.x) {
+      const int h = i / rest, j = rope.dims + i % rest;
+      qr.dst[(size_t)r * qr.ld_dst + (size_t)h * qr.hs_dst + j] = qr.src[(size_t)r * qr.ld_src + (size_t)h * qr.hs_src + j];
+    }
+  }
 }
 
 // grid (rows, heads)
@@ -417,11 +434,12 @@ size_t attn_smem_floats(int H, int D, int R, int TK) {
 }  // namespace
 
 cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, const bf16* w_norm, float eps, const RopeTable& rope,
-                                const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st) {
+                                const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st,
+                                const QueryRope& qr) {
   if (n <= 0) return cudaSuccess;
   if (c.elt_bytes == 4)
-    return launch_k(latent_store_kernel<float>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages);
-  return launch_k(latent_store_kernel<bf16>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages);
+    return launch_k(latent_store_kernel<float>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages, qr);
+  return launch_k(latent_store_kernel<bf16>, dim3(n), dim3(128), 0, st, c, dkv, ld, w_norm, eps, rope, pos, slot, block_table, max_pages, qr);
 }
 
 cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,

@@ -47,8 +47,19 @@ cudaError_t launch_gemm_f32(const GemmF32& g, cudaStream_t st);
 cudaError_t launch_embed_scale_f32(float* x, const bf16* table, const int* ids, int width, int n, float scale, cudaStream_t st);
 // out[r, :] = (res ? res[r, :] : 0) + mult * LN(y[src(r), :]) * w, LN = (y - mean) / sqrt(mean((y - mean)^2) + eps);
 // src(r) = gather ? gather[r] : r.  out may alias res.
+// With `mix` (y == nullptr) the normed vector is the mixture-of-experts combine of row r, computed on the fly:
+// sum_k top_w[r,k] * ye[slot_of[r,k]] (+ sigmoid(z[r, gate_col]) * ys[r]).
+struct MoeMix {
+  const float* ye = nullptr;
+  const int* slot_of = nullptr;
+  const float* top_w = nullptr;
+  int top = 0;
+  const float* ys = nullptr;
+  const float* z = nullptr;
+  int ldz = 0, gate_col = 0;
+};
 cudaError_t launch_layernorm_f32(const float* y, const bf16* w, float* out, const float* res, const int* gather, int width, int n,
-                                 float eps, float mult, cudaStream_t st);
+                                 float eps, float mult, cudaStream_t st, const MoeMix& mix = MoeMix());
 // z = cap * tanh(z / cap) in place
 cudaError_t launch_softcap_f32(float* z, size_t n, float cap, cudaStream_t st);
 cudaError_t launch_cast_f32_bf16(const float* in, bf16* out, size_t n, cudaStream_t st);
@@ -74,9 +85,17 @@ struct RopeTable {
   const float* sin_t = nullptr;
   int dims = 0;  // rotated leading dimensions (pairs (2i, 2i+1))
 };
+// optional rider of launch_latent_store: rotary positions on src[r, h, 0:rot] -> dst[r, h, 0:rot] of the row's query heads
+struct QueryRope {
+  const float* src = nullptr;
+  int ld_src = 0, hs_src = 0;
+  float* dst = nullptr;
+  int ld_dst = 0, hs_dst = 0, heads = 0;
+};
 // per row: latent = rms_unit(dkv[:rank]) * w_norm, key = rope(dkv[rank:], pos) -> cache row (slot, pos)
 cudaError_t launch_latent_store(const LatentCache& c, const float* dkv, int ld, const bf16* w_norm, float eps, const RopeTable& rope,
-                                const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st);
+                                const int* pos, const int* slot, const int* block_table, int max_pages, int n, cudaStream_t st,
+                                const QueryRope& qr = QueryRope());
 // rotary positions on src[r, h, 0:rot] -> dst[r, h, 0:rot] (row strides ld_*, head strides hs_*)
 cudaError_t launch_rope_heads_f32(const float* src, int ld_src, int hs_src, float* dst, int ld_dst, int hs_dst, int heads, int rot,
                                   const RopeTable& rope, const int* pos, int n, cudaStream_t st);

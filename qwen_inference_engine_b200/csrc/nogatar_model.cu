@@ -571,7 +571,9 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_
       c.pool = m->lat_pool, c.elt_bytes = m->f32 ? 4 : 2, c.page_size = e->kv.page_size, c.page_elems = m->page_elems;
       c.layer_off = m->lat_off[L.attn_id], c.rank = k, c.rot = r;
       RopeTable rope{m->rope_cos[L.rope_id], m->rope_sin[L.rope_id], L.rot.dims};
-      NG_TRY(KK_LATENT_STORE, launch_latent_store(c, m->p0 + Nq, ld0, L.dkv_norm, m->eps, rope, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, st));
+      QueryRope qr;  // the rotated part of the query heads goes behind the absorbed part of qa
+      if (r > 0) qr.src = m->p0 + d, qr.ld_src = ld0, qr.hs_src = d + r, qr.dst = m->p1 + k, qr.ld_dst = H * D, qr.hs_dst = D, qr.heads = H;
+      NG_TRY(KK_LATENT_STORE, launch_latent_store(c, m->p0 + Nq, ld0, L.dkv_norm, m->eps, rope, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, st, qr));
       {  // the key up-projection folded into the query: qa[:, h, 0:k] = W_uk,h^T q_h (unrotated part)
         GemmF32 g;
         g.A = m->p0, g.lda = ld0, g.a_batch = d + r;
@@ -580,7 +582,6 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_
         g.M = n, g.N = k, g.K = d, g.batches = H, g.round_a = rnd;
         NG_TRY(KK_F32_PROJ, launch_gemm_f32(g, st));
       }
-      if (r > 0) NG_TRY(KK_LATENT_STORE, launch_rope_heads_f32(m->p0 + d, ld0, d + r, m->p1 + k, H * D, D, H, r, rope, e->pos_d, n, st));
       NG_TRY(KK_LATENT_ATTN, launch_latent_attention(c, m->p1, m->p2, L.sink, L.scale, L.window, H, e->pos_d, e->slot_d, e->block_table_d, e->max_pages_per_seq, n, max_kv_len, m->attn_ws, m->attn_ws_floats, st));
       {  // value up-projection of the attended latent, head by head
         GemmF32 g;
@@ -625,8 +626,12 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_
         NG_TRY(KK_MOE_SHARED, proj(m->x, W, L.w_sup, W, L.shared_ff, m->hs, L.shared_ff, 1, n));
         NG_TRY(KK_MOE_SHARED, proj(m->hs, L.shared_ff, L.w_sdown, L.shared_ff, W, m->ys, W, 0, n));
       }
-      NG_TRY(KK_MOE_COMBINE, launch_moe_combine(m->ye, m->slot_of, m->top_w, top, L.shared_ff > 0 ? m->ys : nullptr, m->zr, ldz, E, m->y, W, n, st));
-      NG_TRY(KK_F32_NORM, launch_layernorm_f32(m->y, L.norm2, m->x, m->x, nullptr, W, n, m->eps, m->res_mult, st));
+      {  // combine folded into the output norm
+        MoeMix mix;
+        mix.ye = m->ye, mix.slot_of = m->slot_of, mix.top_w = m->top_w, mix.top = top, mix.ys = L.shared_ff > 0 ? m->ys : nullptr;
+        mix.z = m->zr, mix.ldz = ldz, mix.gate_col = E;
+        NG_TRY(KK_F32_NORM, launch_layernorm_f32(nullptr, L.norm2, m->x, m->x, nullptr, W, n, m->eps, m->res_mult, st, mix));
+      }
     }
     if (m->dump_layers)
       if (cudaMemcpyAsync(m->layer_dump + li * (size_t)e->opts.max_batch_tokens * W, m->x, (size_t)n * W * sizeof(float), cudaMemcpyDeviceToDevice, st) != cudaSuccess)

@@ -30,18 +30,30 @@ __global__ void embed_scale_kernel(float* __restrict__ x, const bf16* __restrict
 }
 
 __global__ void layernorm_f32_kernel(const float* __restrict__ y, const bf16* __restrict__ w, float* out, const float* res,
-                                     const int* __restrict__ gather, int width, float eps, float mult) {
+                                     const int* __restrict__ gather, int width, float eps, float mult, const MoeMix mix) {
   extern __shared__ float row[];
   __shared__ float red[32];
   pdl_wait();
   pdl_trigger();
   const int r = blockIdx.x;
-  const float* src = y + (size_t)(gather ? gather[r] : r) * width;
   float s = 0.f;
-  for (int i = threadIdx.x; i < width; i += blockDim.x) {
-    const float v = src[i];
-    row[i] = v;
-    s += v;
+  if (y) {
+    const float* src = y + (size_t)(gather ? gather[r] : r) * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      const float v = src[i];
+      row[i] = v;
+      s += v;
+    }
+  } else {  // the experts' outputs of this row, weighted, plus the gated shared expert
+    const float sg = mix.ys ? 1.0f / (1.0f + expf(-mix.z[(size_t)r * mix.ldz + mix.gate_col])) : 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float a = 0.f;
+      for (int k = 0; k < mix.top; ++k)
+        a = fmaf(mix.top_w[(size_t)r * mix.top + k], mix.ye[(size_t)mix.slot_of[(size_t)r * mix.top + k] * width + i], a);
+      if (mix.ys) a = fmaf(sg, mix.ys[(size_t)r * width + i], a);
+      row[i] = a;
+      s += a;
+    }
   }
   const float mean = block_sum(s, red) / (float)width;
   float q = 0.f;
@@ -544,14 +556,14 @@ cudaError_t launch_embed_scale_f32(float* x, const bf16* table, const int* ids, 
 }
 
 cudaError_t launch_layernorm_f32(const float* y, const bf16* w, float* out, const float* res, const int* gather, int width, int n,
-                                 float eps, float mult, cudaStream_t st) {
+                                 float eps, float mult, cudaStream_t st, const MoeMix& mix) {
   if (n <= 0) return cudaSuccess;
   const size_t smem = (size_t)width * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t r = cudaFuncSetAttribute(layernorm_f32_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (r != cudaSuccess) return r;
   }
-  return launch_k(layernorm_f32_kernel, dim3(n), dim3(256), smem, st, y, w, out, res, gather, width, eps, mult);
+  return launch_k(layernorm_f32_kernel, dim3(n), dim3(256), smem, st, y, w, out, res, gather, width, eps, mult, mix);
 }
 
 cudaError_t launch_softcap_f32(float* z, size_t n, float cap, cudaStream_t st) {
