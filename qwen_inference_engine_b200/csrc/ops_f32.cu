@@ -295,9 +295,21 @@ __global__ void __launch_bounds__(256) gemm_skinny_f32_kernel(const GemmF32 g) {
   for (int k0 = 0; k0 < g.K; k0 += SKINNY_KC) {
     const int kc = min(SKINNY_KC, g.K - k0);
     __syncthreads();
-    for (int i = threadIdx.x; i < NP * kc; i += 256) {
-      const int n = i / kc, k = i % kc;  // k fastest: coalesced weight reads
-      s_w[k * NP + n] = n < g.N ? bf2f(g.W[(size_t)n * g.ldw + k0 + k]) : 0.f;
+    if (g.ldw % 8 == 0 && kc % 8 == 0 && k0 % 8 == 0 && (reinterpret_cast<uintptr_t>(g.W) & 15) == 0) {
+      const int kv = kc / 8;  // 16-byte pieces per weight row
+      for (int i = threadIdx.x; i < NP * kv; i += 256) {
+        const int n = i / kv, k = (i % kv) * 8;
+        uint4 wv = make_uint4(0, 0, 0, 0);
+        if (n < g.N) wv = *reinterpret_cast<const uint4*>(g.W + (size_t)n * g.ldw + k0 + k);
+        const float wf[8] = {lo2f(wv.x), hi2f(wv.x), lo2f(wv.y), hi2f(wv.y), lo2f(wv.z), hi2f(wv.z), lo2f(wv.w), hi2f(wv.w)};
+#pragma unroll
+        for (int u = 0; u < 8; ++u) s_w[(k + u) * NP + n] = wf[u];
+      }
+    } else {
+      for (int i = threadIdx.x; i < NP * kc; i += 256) {
+        const int n = i / kc, k = i % kc;  // k fastest: coalesced weight reads
+        s_w[k * NP + n] = n < g.N ? bf2f(g.W[(size_t)n * g.ldw + k0 + k]) : 0.f;
+      }
     }
     __syncthreads();
 #pragma unroll
@@ -305,6 +317,7 @@ __global__ void __launch_bounds__(256) gemm_skinny_f32_kernel(const GemmF32 g) {
       const int m = m_base + warp + 8 * r;
       if (m >= g.M) continue;
       const float* a = g.A + (size_t)m * g.lda + k0;
+#pragma unroll 4
       for (int k = lane; k < kc; k += 32) {
         float av = a[k];
         if (g.round_a) av = bf2f(f2bf(av));
