@@ -113,13 +113,13 @@ __global__ void __launch_bounds__(128) mlstm_scan_kernel(const MlstmArgs a, int 
 // raw outputs S^T q / denominator go to `out`; the per-head unit norm, norm weight and output gate follow in
 // mlstm_out_kernel because they need all columns of the head.
 template <int DPT>
-__global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) {
-  constexpr int CH = 16;  // tokens staged per chunk
+__global__ void __launch_bounds__(288) mlstm_scan_reg_kernel(const MlstmArgs a) {
+  constexpr int CH = 16, NW = 8, NT = NW * 32;  // tokens staged per chunk; compute warps (a ninth warp finishes tokens)  // tokens staged per chunk
   // [2][CH][stride]: q (scaled, zero-padded to 4 * DPT) | k (same) | v of this CTA's 32 columns | log input gate | log forget gate
   extern __shared__ float4 s_in4[];
   float* s_in = reinterpret_cast<float*>(s_in4);
-  __shared__ float s_part[2][4][32];
-  __shared__ float s_dot[2][4];
+  __shared__ float s_part[2][NW][32];
+  __shared__ float s_dot[2][NW];
   pdl_wait();
   pdl_trigger();
   const int d = a.dim, vd = a.vdim, H = a.heads;
@@ -134,7 +134,8 @@ __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) 
   const int nblk = gridDim.z;
   float* ng = st + (size_t)H * d * vd + ((size_t)h * nblk + blockIdx.z) * d;
   float* mg = st + (size_t)H * d * vd + (size_t)H * nblk * d + (size_t)h * nblk + blockIdx.z;
-  const int i0 = w * DPT;
+  const bool outw = w == NW;  // the last warp only finishes tokens: sums the partial results, divides, stores
+  const int i0 = outw ? d : w * DPT;
   float S[DPT], nn[DPT];
 #pragma unroll
   for (int i = 0; i < DPT; ++i) {
@@ -145,8 +146,8 @@ __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) 
   float m = *mg;
   const float qs = rsqrtf((float)d);
   const int ld = a.ld;
-  constexpr int DQ = 4 * DPT, stride = 2 * DQ + 36;  // a multiple of 4 floats: rows are read with 16-byte loads
-  constexpr int PER = (stride + 127) / 128;         // staged elements of one token per thread
+  constexpr int DQ = NW * DPT, stride = 2 * DQ + 36;  // a multiple of 4 floats: rows are read with 16-byte loads
+  constexpr int PER = (stride + NT - 1) / NT;       // staged elements of one token per thread
   float stage[CH][PER];
   // the inputs of chunk c: global -> registers (in flight while the previous chunk is computed) -> shared memory
   auto fetch = [&](int c) {
@@ -156,7 +157,7 @@ __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) 
       const float* row = a.qkvg + (size_t)min(r, r1 - 1) * ld;
 #pragma unroll
       for (int u = 0; u < PER; ++u) {
-        const int j = tid + u * 128;
+        const int j = tid + u * NT;
         float v = 0.f;
         if (j < DQ) v = j < d ? row[h * d + j] * qs : 0.f;
         else if (j < 2 * DQ) v = j - DQ < d ? row[H * d + h * d + (j - DQ)] : 0.f;
@@ -173,54 +174,61 @@ __global__ void __launch_bounds__(128) mlstm_scan_reg_kernel(const MlstmArgs a) 
     for (int t = 0; t < CH; ++t)
 #pragma unroll
       for (int u = 0; u < PER; ++u) {
-        const int j = tid + u * 128;
+        const int j = tid + u * NT;
         if (j < stride) dst[t * stride + j] = stage[t][u];
       }
   };
   const int n_chunks = (r1 - r0 + CH - 1) / CH;
-  fetch(0);
-  put(0);
+  if (!outw) {
+    fetch(0);
+    put(0);
+  }
   __syncthreads();
   int par = 0;
   for (int c = 0; c < n_chunks; ++c) {
-    if (c + 1 < n_chunks) fetch(c + 1);
+    if (c + 1 < n_chunks && !outw) fetch(c + 1);
     const float* in = s_in + (size_t)(c & 1) * CH * stride;
     const int nt = min(CH, r1 - r0 - c * CH);
     for (int t = 0; t < nt; ++t) {
       const float* tk = in + t * stride;
-      const float ig = tk[2 * DQ + 32], fg = tk[2 * DQ + 33], v = tk[2 * DQ + lane];
-      const float4* q4 = reinterpret_cast<const float4*>(tk + i0);
-      const float4* k4 = reinterpret_cast<const float4*>(tk + DQ + i0);
+      const float ig = tk[2 * DQ + 32], fg = tk[2 * DQ + 33];
       const float m_new = fmaxf(fg + m, ig);
-      const float ea = expf(fg + m - m_new), eb = expf(ig - m_new);
-      const float bv = eb * v;
-      float acc = 0.f, dpart = 0.f;
+      if (!outw) {
+        const float v = tk[2 * DQ + lane];
+        const float4* q4 = reinterpret_cast<const float4*>(tk + i0);
+        const float4* k4 = reinterpret_cast<const float4*>(tk + DQ + i0);
+        const float ea = expf(fg + m - m_new), eb = expf(ig - m_new);
+        const float bv = eb * v;
+        float acc = 0.f, dpart = 0.f;
 #pragma unroll
-      for (int i4 = 0; i4 < DPT / 4; ++i4) {
-        const float4 qv = q4[i4], kv = k4[i4];
-        const float q[4] = {qv.x, qv.y, qv.z, qv.w}, k[4] = {kv.x, kv.y, kv.z, kv.w};
+        for (int i4 = 0; i4 < DPT / 4; ++i4) {
+          const float4 qv = q4[i4], kv = k4[i4];
+          const float q[4] = {qv.x, qv.y, qv.z, qv.w}, k[4] = {kv.x, kv.y, kv.z, kv.w};
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-          const int i = i4 * 4 + u;
-          S[i] = fmaf(ea, S[i], k[u] * bv);
-          acc = fmaf(S[i], q[u], acc);
-          nn[i] = fmaf(ea, nn[i], eb * k[u]);
-          dpart = fmaf(nn[i], q[u], dpart);  // the same in every lane of the warp
+          for (int u = 0; u < 4; ++u) {
+            const int i = i4 * 4 + u;
+            S[i] = fmaf(ea, S[i], k[u] * bv);
+            acc = fmaf(S[i], q[u], acc);
+            nn[i] = fmaf(ea, nn[i], eb * k[u]);
+            dpart = fmaf(nn[i], q[u], dpart);  // the same in every lane of the warp
+          }
         }
+        s_part[par][w][lane] = acc;
+        if (lane == 0) s_dot[par][w] = dpart;
       }
-      s_part[par][w][lane] = acc;
-      if (lane == 0) s_dot[par][w] = dpart;
       __syncthreads();  // one barrier per token: the partial sums alternate between two buffers
-      if (w == 0) {
-        const float dot = (s_dot[par][0] + s_dot[par][1]) + (s_dot[par][2] + s_dot[par][3]);
+      if (outw) {
+        float dot = 0.f, num = 0.f;
+#pragma unroll
+        for (int x = 0; x < NW; ++x) dot += s_dot[par][x], num += s_part[par][x][lane];
         const float den = fmaxf(fabsf(dot), expf(-m_new)) + 1e-6f;
-        const float o = ((s_part[par][0][lane] + s_part[par][1][lane]) + (s_part[par][2][lane] + s_part[par][3][lane])) / den;
+        const float o = num / den;
         if (col_ok) a.out[(size_t)(r0 + c * CH + t) * H * vd + h * vd + col] = o;
       }
       par ^= 1;
       m = m_new;
     }
-    if (c + 1 < n_chunks) put(c + 1);
+    if (c + 1 < n_chunks && !outw) put(c + 1);
     __syncthreads();
   }
 #pragma unroll
@@ -266,13 +274,12 @@ cudaError_t launch_mlstm_scan(const MlstmArgs& a, cudaStream_t st) {
     const dim3 grid(a.n_seg, a.heads, (a.vdim + 31) / 32);
     cudaError_t rg = launch_k(mlstm_gates_kernel, dim3((a.n_rows * 2 * a.heads + 255) / 256), dim3(256), 0, st, a.gates, a.n_rows, a.heads, a.gate_cap);
     if (rg != cudaSuccess) return rg;
-    const int dpt = a.dim <= 16 ? 4 : a.dim <= 32 ? 8 : a.dim <= 64 ? 16 : 32;
-    const size_t smem = (size_t)2 * 16 * (8 * dpt + 36) * sizeof(float);  // two chunks of 16 staged tokens (<= 37 KB)
+    const int dpt = a.dim <= 32 ? 4 : a.dim <= 64 ? 8 : 16;  // rows of S per thread: 8 compute warps split dim
+    const size_t smem = (size_t)2 * 16 * (16 * dpt + 36) * sizeof(float);  // two chunks of 16 staged tokens (<= 37 KB)
     cudaError_t r;
-    if (a.dim <= 16) r = launch_k(mlstm_scan_reg_kernel<4>, grid, dim3(128), smem, st, a);
-    else if (a.dim <= 32) r = launch_k(mlstm_scan_reg_kernel<8>, grid, dim3(128), smem, st, a);
-    else if (a.dim <= 64) r = launch_k(mlstm_scan_reg_kernel<16>, grid, dim3(128), smem, st, a);
-    else r = launch_k(mlstm_scan_reg_kernel<32>, grid, dim3(128), smem, st, a);
+    if (a.dim <= 32) r = launch_k(mlstm_scan_reg_kernel<4>, grid, dim3(288), smem, st, a);
+    else if (a.dim <= 64) r = launch_k(mlstm_scan_reg_kernel<8>, grid, dim3(288), smem, st, a);
+    else r = launch_k(mlstm_scan_reg_kernel<16>, grid, dim3(288), smem, st, a);
     if (r != cudaSuccess) return r;
     return launch_k(mlstm_out_kernel, dim3(a.n_rows, a.heads), dim3(128), 0, st, a);
   }
