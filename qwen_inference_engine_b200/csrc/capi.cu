@@ -395,7 +395,11 @@ static void engine_free(qie_engine* e) {
     if (kvp.second.exec) cudaGraphExecDestroy(kvp.second.exec);
   for (auto& kvp : e->cap)
     if (kvp.second.d) cudaFree(kvp.second.d);
-  nogatar_free(e);
+  if (e->fam) {
+    e->fam->release();
+    delete e->fam;
+    e->fam = nullptr, e->ng = nullptr, e->fv = nullptr;
+  }
   if (!e->blob_owned) e->blob = nullptr;
   void* dev[] = {e->blob, e->cos_d, e->sin_d, e->kv.pool, e->block_table_d, e->ids_d, e->pos_d, e->slot_d,
                  e->sampled_d, e->rowstep_d, e->x, e->xn, e->q, e->k, e->v, e->att, e->h, e->logits, e->qkv,
@@ -932,7 +936,7 @@ int qie_engine_set_sampling(qie_engine* e, int topk, float temperature_prefill, 
 
 int qie_engine_set_repetition_penalty(qie_engine* e, float penalty) {
   if (!e || !(penalty > 0.0f)) return fail(QIE_EINVAL, "repetition penalty must be > 0");
-  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "repetition penalty");
+  if (e->fam) return fail(QIE_EINVAL, "%s: not available for the %s family", "repetition penalty", e->fam->family_name());
   if (e->opts.tp_size > 1 && penalty != 1.0f) return fail(QIE_EINVAL, "repetition penalty over a sharded vocabulary is not built");
   CU(cudaSetDevice(e->opts.device));
   CU(cudaStreamSynchronize(e->stream));
@@ -955,7 +959,7 @@ int qie_seq_new(qie_engine* e, int* seq) {
       e->seqs[i] = Sequence();
       e->seqs[i].live = true;
       *seq = i;
-      if (e->ng) nogatar_reset_slot(e, i);  // recurrent state of the slot's previous user
+      if (e->fam) e->fam->reset_slot(e, i);  // recurrent state of the slot's previous user
       return QIE_OK;
     }
   return fail(QIE_ENOMEM, "all %zu sequence slots are live", e->seqs.size());
@@ -1018,7 +1022,7 @@ int qie_prefill(qie_engine* e, int seq, const int32_t* h_ids, int n, int32_t* h_
   CU(cudaSetDevice(e->opts.device));
   Sequence& s = e->seqs[seq];
   if (s.host_copy) return fail(QIE_ESTATE, "sequence %d is swapped out (qie_seq_swap_in first)", seq);
-  if (e->ng) {  // families with a general row forward: a prompt is one entry of a batch
+  if (e->fam) {  // families with a general row forward: a prompt is one entry of a batch
     const int want = n - 1;
     rc = qie_forward_batch(e, 1, &seq, &n, h_ids, 1, &want, nullptr, h_token);
     if (rc == QIE_OK) e->seqs[seq].step += 1;
@@ -1057,7 +1061,7 @@ int qie_prefill(qie_engine* e, int seq, const int32_t* h_ids, int n, int32_t* h_
 
 // one decode step for the batch already staged on the device (ids/pos/slot/rowstep)
 static cudaError_t decode_forward(qie_engine* e, int n, int bucket) {
-  if (e->ng) return nogatar_forward(e, n, n, n, bucket, e->temp_decode, true);  // one row and one segment per sequence
+  if (e->fam) return e->fam->forward(e, n, n, n, bucket, e->temp_decode, true);  // one row and one segment per sequence
   if (decode_uses_mega(e, n, bucket)) {
     cudaError_t r = forward_decode_mega(e, n, bucket, e->temp_decode);
     if (r != cudaErrorNotReady) return r;  // NotReady: the cooperative launch could not be placed, nothing ran yet
@@ -1212,7 +1216,7 @@ int qie_sync(qie_engine* e) {
 
 int qie_capture_enable(qie_engine* e, int on) {
   if (!e) return fail(QIE_EINVAL, "null engine");
-  if (e->ng && on) return fail(QIE_EINVAL, "capture: the Nogatar family keeps the residual stream per layer instead (set_int dump_layers)");
+  if (e->fam && on) return fail(QIE_EINVAL, "capture: the %s family keeps the residual stream per layer instead (set_int dump_layers)", e->fam->family_name());
   e->capture = on != 0;
   return QIE_OK;
 }
@@ -1236,7 +1240,7 @@ long qie_launch_count(const qie_engine* e) { return e ? e->launches : 0; }
 int qie_seq_swap_out(qie_engine* e, int seq) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
-  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "swap_out");
+  if (e->fam) return fail(QIE_EINVAL, "%s: not available for the %s family", "swap_out", e->fam->family_name());
   Sequence& s = e->seqs[seq];
   if (s.host_copy) return fail(QIE_ESTATE, "sequence %d is already swapped out", seq);
   if (s.pages.empty()) return QIE_OK;
@@ -1256,7 +1260,7 @@ int qie_seq_swap_out(qie_engine* e, int seq) {
 int qie_seq_swap_in(qie_engine* e, int seq) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
-  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "swap_in");
+  if (e->fam) return fail(QIE_EINVAL, "%s: not available for the %s family", "swap_in", e->fam->family_name());
   Sequence& s = e->seqs[seq];
   if (!s.host_copy) return fail(QIE_ESTATE, "sequence %d is not swapped out", seq);
   if ((int)e->free_pages.size() < s.host_pages) return fail(QIE_ENOMEM, "swap_in: %d pages needed, %zu free", s.host_pages, e->free_pages.size());
@@ -1285,7 +1289,7 @@ int qie_seq_swap_in(qie_engine* e, int seq) {
 static int seq_kv_copy(qie_engine* e, int seq, int pos0, int n, qie_bf16* h_K, qie_bf16* h_V, bool write) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
-  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "seq_kv read / write");
+  if (e->fam) return fail(QIE_EINVAL, "%s: not available for the %s family", "seq_kv read / write", e->fam->family_name());
   if (n <= 0 || pos0 < 0 || !h_K || !h_V) return fail(QIE_EINVAL, "seq_kv: bad range or null buffers");
   Sequence& s = e->seqs[seq];
   if (s.host_copy) return fail(QIE_ESTATE, "sequence %d is swapped out", seq);
@@ -1336,7 +1340,7 @@ int qie_seq_kv_write(qie_engine* e, int seq, int pos0, int n, const qie_bf16* h_
 int qie_seq_fill_synthetic(qie_engine* e, int seq, int n_pos, uint64_t seed) {
   int rc = check_seq(e, seq);
   if (rc) return rc;
-  if (e->ng) return fail(QIE_EINVAL, "%s: not available for the Nogatar family", "fill_synthetic");
+  if (e->fam) return fail(QIE_EINVAL, "%s: not available for the %s family", "fill_synthetic", e->fam->family_name());
   if (n_pos <= 0) return fail(QIE_EINVAL, "fill_synthetic: n_pos must be > 0");
   CU(cudaSetDevice(e->opts.device));
   Sequence& s = e->seqs[seq];
@@ -1355,8 +1359,8 @@ int qie_engine_set_int(qie_engine* e, const char* key, long value) {
   if (!e || !key) return fail(QIE_EINVAL, "null argument");
   std::string k(key);
   if (k == "dump_layers") {
-    if (!e->ng) return fail(QIE_EINVAL, "dump_layers: Nogatar family only");
-    e->ng->dump_layers = value != 0;
+    if (!e->fam) return fail(QIE_EINVAL, "dump_layers: families with an fp32 residual stream only");
+    e->fam->dump_layers = value != 0;
   } else if (k == "mega") e->use_mega = value != 0;
   else if (k == "gemv") e->use_gemv = value != 0;
   else if (k == "gemv_dataflow") e->gemv_dataflow = value;
@@ -1395,11 +1399,11 @@ long qie_engine_read_activation(qie_engine* e, const char* name, void* h_out, si
   const size_t R = e->opts.max_batch_tokens;
   const size_t Dq = (size_t)c.n_q * c.head_dim, Dkv = (size_t)c.n_kv * c.head_dim;
   std::string k(name);
-  if (e->ng) {  // "layers": the fp32 residual stream after every layer of the last forward, [layers][max_batch_tokens][width]; "logits_f32"
-    const NgModel* m = e->ng;
+  if (e->fam) {  // "layers": the fp32 residual stream after every layer of the last forward, [layers][max_batch_tokens][width]; "logits_f32"
+    const RowFamily* m = e->fam;
     const void* p = nullptr;
     size_t nb = 0;
-    if (k == "layers" && m->layer_dump) p = m->layer_dump, nb = m->layers.size() * R * m->width * sizeof(float);
+    if (k == "layers" && m->layer_dump) p = m->layer_dump, nb = m->layer_runs() * R * m->width * sizeof(float);
     else if (k == "logits_f32") p = m->logits, nb = R * (size_t)m->vocab * sizeof(float);
     else if (k == "sampled") p = e->sampled_d, nb = R * sizeof(int);
     if (!p) return fail(QIE_EINVAL, "unknown activation %s", name);
@@ -1438,7 +1442,8 @@ long qie_engine_write_activation(qie_engine* e, const char* name, const void* h_
 const char* qie_kernel_kind_name(int kind) {
   static const char* names[KK_COUNT] = {"embedding", "rmsnorm", "gemm_qkv", "qkv_post", "attention", "gemm_o",
                                         "gemm_gateup", "gemm_down", "lm_head", "sample", "advance", "f32_norm", "f32_proj", "latent_store",
-                                        "latent_attn", "mlstm_scan", "moe_route", "moe_experts", "moe_shared", "moe_combine"};
+                                        "latent_attn", "mlstm_scan", "moe_route", "moe_experts", "moe_shared", "moe_combine", "hyper_streams", "kv_store",
+                                        "gqa_attn", "causal_conv", "lru_scan", "ssd_scan", "glu_act"};
   return kind >= 0 && kind < KK_COUNT ? names[kind] : nullptr;
 }
 
@@ -1446,7 +1451,7 @@ int qie_decode_step_profile(qie_engine* e, const int* h_seqs, const int32_t* h_t
                             int* launches_by_kind, int n_kinds) {
   if (!h_tokens_in || !ms_by_kind || !launches_by_kind || n_kinds < KK_COUNT)
     return fail(QIE_EINVAL, "decode_step_profile: need %d kinds", (int)KK_COUNT);
-  if (e && e->ng) return fail(QIE_EINVAL, "decode_step_profile: not available for the Nogatar family");
+  if (e && e->fam) return fail(QIE_EINVAL, "decode_step_profile: not available for the %s family (qie_profile_begin / end)", e->fam->family_name());
   int mk = 0;
   int rc = decode_prepare(e, h_seqs, n, &mk);
   if (rc) return rc;
@@ -1486,13 +1491,15 @@ int qie_decode_step_profile(qie_engine* e, const int* h_seqs, const int32_t* h_t
 // model registry + the general batch forward
 const char* qie_model_families(void) { return registry_names(); }
 
-const char* qie_engine_family(const qie_engine* e) { return !e ? "" : (e->ng ? "nogatar" : "qwen"); }
+const char* qie_engine_family(const qie_engine* e) { return !e ? "" : (e->fam ? e->fam->family_name() : "qwen"); }
 
 static int create_family(qie_engine* e, int family, const std::string& arg, bool synthetic, uint64_t seed) {
-  if (family != FAMILY_NOGATAR) return fail(QIE_EINVAL, "family not handled here");
-  if (e->opts.tp_size > 1) return fail(QIE_EINVAL, "the Nogatar family is not sharded (tp_size must be 1)");
+  if (family != FAMILY_NOGATAR && family != FAMILY_FOSAVIK) return fail(QIE_EINVAL, "family not handled here");
+  if (e->opts.tp_size > 1) return fail(QIE_EINVAL, "this family is not sharded (tp_size must be 1)");
   int code = QIE_EIO;
-  const std::string err = synthetic ? nogatar_create_synthetic(e, arg, seed, &code) : nogatar_create(e, arg, &code);
+  std::string err;
+  if (family == FAMILY_NOGATAR) err = synthetic ? nogatar_create_synthetic(e, arg, seed, &code) : nogatar_create(e, arg, &code);
+  else err = synthetic ? fosavik_create_synthetic(e, arg, seed, &code) : fosavik_create(e, arg, &code);
   if (!err.empty()) return fail(code, "%s", err.c_str());
   return QIE_OK;
 }
@@ -1533,7 +1540,7 @@ int qie_engine_create_synthetic_json(const char* config_json, uint64_t seed, con
   std::string arch, err;
   const int family = registry_family_of_config(config_json, &arch, &err);
   if (family < 0) return fail(QIE_EIO, "%s", err.c_str());
-  if (family != FAMILY_NOGATAR) return fail(QIE_EINVAL, "synthetic weights from a configuration text: Nogatar family (Qwen: qie_engine_create_synthetic)");
+  if (family == FAMILY_QWEN) return fail(QIE_EINVAL, "synthetic weights from a configuration text: not for the Qwen family (qie_engine_create_synthetic)");
   qie_engine* e = nullptr;
   int rc = engine_begin(opts, &e);
   if (rc) return rc;
@@ -1551,10 +1558,10 @@ int qie_engine_create_synthetic_json(const char* config_json, uint64_t seed, con
 int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int* h_counts, const int32_t* h_tokens, int n_want,
                       const int* h_want_rows, float* h_logits, int32_t* h_sampled) {
   if (!e || n_entries <= 0 || !h_seqs || !h_counts || !h_tokens) return fail(QIE_EINVAL, "forward_batch: null argument or empty batch");
-  if (!e->ng) return fail(QIE_EINVAL, "forward_batch: this family has no general row forward (use qie_prefill / qie_decode_step)");
+  if (!e->fam) return fail(QIE_EINVAL, "forward_batch: this family has no general row forward (use qie_prefill / qie_decode_step)");
   if (n_want < 0 || (n_want > 0 && !h_want_rows)) return fail(QIE_EINVAL, "forward_batch: bad want list");
   CU(cudaSetDevice(e->opts.device));
-  NgModel* m = e->ng;
+  RowFamily* m = e->fam;
   const int R = e->opts.max_batch_tokens;
   long total = 0;
   for (int i = 0; i < n_entries; ++i) {
@@ -1617,7 +1624,7 @@ int qie_forward_batch(qie_engine* e, int n_entries, const int* h_seqs, const int
     CU(cudaMemcpyAsync(m->seg_start, seg_start.data(), (n_seg + 1) * sizeof(int), cudaMemcpyHostToDevice, e->stream));
     CU(cudaMemcpyAsync(m->seg_slot, seg_slot.data(), n_seg * sizeof(int), cudaMemcpyHostToDevice, e->stream));
     if (n_out) CU(cudaMemcpyAsync(m->out_rows, out_rows.data(), n_out * sizeof(int), cudaMemcpyHostToDevice, e->stream));
-    CU(nogatar_forward(e, n, n_seg, n_out, max_kv, e->temp_prefill, false));
+    CU(m->forward(e, n, n_seg, n_out, max_kv, e->temp_prefill, false));
     if (n_out && h_logits)
       CU(cudaMemcpyAsync(h_logits + (size_t)want0 * e->cfg.vocab, m->logits, (size_t)n_out * e->cfg.vocab * sizeof(float), cudaMemcpyDeviceToHost, e->stream));
     if (n_out && h_sampled) CU(cudaMemcpyAsync(h_sampled + want0, e->sampled_d, n_out * sizeof(int), cudaMemcpyDeviceToHost, e->stream));

@@ -13,6 +13,7 @@
 
 #include "checkpoint.h"
 #include "kernels.h"
+#include "fosavik.h"
 #include "nogatar.h"
 #include "tp_nccl.h"
 
@@ -42,9 +43,11 @@ struct CaptureBuf {
 }  // namespace qie
 
 struct qie_engine {
-  // model family: Qwen (the members below named after its operators) unless `ng` is set (nogatar.h); sequences, pages,
+  // model family: Qwen (the members below named after its operators) unless `fam` is set (nogatar.h, fosavik.h); sequences, pages,
   // block tables, row metadata, sampling and graphs are shared by the families
+  qie::RowFamily* fam = nullptr;  // the family's interface (family.h); ng / fv below are the same object, typed
   qie::NgModel* ng = nullptr;
+  qie::FvModel* fv = nullptr;
   qie_config cfg{};
   qie_engine_opts opts{};
   int num_sms = 0;
@@ -167,6 +170,8 @@ enum KernelKind {
   KK_LM_HEAD, KK_SAMPLE, KK_ADVANCE,
   // classes of the fp32-stream families (nogatar_model.cu)
   KK_F32_NORM, KK_F32_PROJ, KK_LATENT_STORE, KK_LATENT_ATTN, KK_MLSTM, KK_MOE_ROUTE, KK_MOE_EXPERTS, KK_MOE_SHARED, KK_MOE_COMBINE,
+  // fosavik_model.cu
+  KK_HYPER, KK_KV_STORE, KK_GQA_ATTN, KK_CONV, KK_LRU_SCAN, KK_SSD_SCAN, KK_GLU,
   KK_COUNT
 };
 // one forward over n_rows rows already described in ids_d/pos_d/slot_d; logits for rows

@@ -21,6 +21,7 @@ struct Row {
 };
 const Row kRegistry[] = {
     {"Nogatar", FAMILY_NOGATAR},
+    {"Fosavik", FAMILY_FOSAVIK},
     {"Qwen2ForCausalLM", FAMILY_QWEN},
     {"Qwen3ForCausalLM", FAMILY_QWEN},
 };

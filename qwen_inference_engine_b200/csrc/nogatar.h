@@ -12,6 +12,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "family.h"
 
 struct qie_engine;
 
@@ -38,6 +39,7 @@ struct GemmF32 {
   const int* grp_off = nullptr;
   const int* row_idx = nullptr;
   const bf16* bias = nullptr;  // [N] added before the activation
+  long bias_batch = 0;         // elements between the bias vectors of consecutive problems
   int act = 0;                 // 0 none, 1 relu(z)^2
   int round_a = 0;             // 1: A is rounded to bf16 before the product (bf16 serving precision)
   int round_c = 0;             // 1: the result is rounded to bf16 (still stored as fp32)
@@ -170,14 +172,18 @@ struct NgLayer {
   const bf16 *wqkvg = nullptr, *wif = nullptr, *bif = nullptr, *out_norm = nullptr;
   const bf16 *w_up = nullptr, *w_down = nullptr, *w_router = nullptr, *w_sup = nullptr, *w_sdown = nullptr;
 };
-struct NgModel {
-  int vocab = 0, width = 0;
+struct NgModel : RowFamily {
+  const char* family_name() const override { return "nogatar"; }
+  cudaError_t forward(qie_engine* e, int n, int n_seg, int n_out, int max_kv_len, float temperature, bool advance) override;
+  void reset_slot(qie_engine* e, int seq) override;
+  void release() override;
+  size_t layer_runs() const override { return layers.size(); }
+
   float embed_scale = 1.f, eps = 1e-6f, res_mult = 1.f, softcap = 0.f;
   std::vector<NgLayer> layers;
   const bf16 *embed = nullptr, *final_norm = nullptr, *head = nullptr;
   bf16* blob = nullptr;
   size_t blob_bytes = 0;
-  bool f32 = false;  // true 32-bit arithmetic everywhere; false: bf16 products / bf16 cache rows
   // rotary tables, one per distinct configuration
   std::vector<NgRot> rope_cfg;
   std::vector<float*> rope_cos, rope_sin;
@@ -193,25 +199,13 @@ struct NgModel {
   // x: residual stream, y: sublayer output, p0..p3: projections of the mixers, zr/top_*: router, he/ye: expert
   // hidden and output rows grouped by expert, hs/ys: shared expert, xo: normed output rows
   float *x = nullptr, *y = nullptr, *p0 = nullptr, *p1 = nullptr, *p2 = nullptr, *p3 = nullptr, *zr = nullptr, *top_w = nullptr;
-  float *he = nullptr, *ye = nullptr, *hs = nullptr, *ys = nullptr, *xo = nullptr, *logits = nullptr;
+  float *he = nullptr, *ye = nullptr, *hs = nullptr, *ys = nullptr, *xo = nullptr;
   int *top_idx = nullptr, *grp_off = nullptr, *perm_row = nullptr, *slot_of = nullptr;
-  int *seg_start = nullptr, *seg_slot = nullptr, *out_rows = nullptr;
-  // bf16 serving precision, more than 16 rows: projections run on the tcgen05 GEMM (gemm_tcgen05.cu) between two
-  // conversion kernels; ab / cb are its dense bf16 operand and result, tc_maps the weight descriptors by pointer
-  bool use_tc = true;
-  bf16 *ab = nullptr, *cb = nullptr;
-  float* tc_ws = nullptr;
-  size_t tc_ws_bytes = 0;
-  int* tc_counters = nullptr;
-  void* tc_maps = nullptr;  // std::map<const bf16*, TensorMap2D>*
+  // bf16 serving precision, more than 16 rows: projections run on the tcgen05 GEMM between two conversion kernels
+  TcProjector tc;
   float* attn_ws = nullptr;  // partial results of the key-split attention of small batches
   size_t attn_ws_floats = 0;
-  int* iota = nullptr;  // 0, 1, 2, ...: segments and output rows of a decode step (one row per sequence)
   int max_experts = 0;
-  bf16* logits_bf = nullptr;
-  // parity hook: residual stream after every layer of the last forward [layers, rows, width]
-  float* layer_dump = nullptr;
-  bool dump_layers = false;
 };
 
 // reads <dir>/config.json and <dir>/model.safetensors; fills e->ng and the engine's shared parts (page pool
@@ -219,11 +213,5 @@ struct NgModel {
 std::string nogatar_create(qie_engine* e, const std::string& dir, int* code);
 // same model over generated weights (bench / tests): cfg_json is the text of a config.json
 std::string nogatar_create_synthetic(qie_engine* e, const std::string& cfg_json, uint64_t seed, int* code);
-void nogatar_free(qie_engine* e);
-void nogatar_reset_slot(qie_engine* e, int seq);
-// one forward over n rows (ids_d / pos_d / slot_d staged; segments and output rows staged in ng) -> ng->logits
-// [n_out, vocab] and sampled_d[0..n_out)
-// max_kv_len bounds position + 1 over the rows (grid sizing of the attention)
-cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_kv_len, float temperature, bool advance);
 
 }  // namespace qie

@@ -19,26 +19,6 @@
 namespace qie {
 namespace {
 
-struct TensorSpec {
-  std::string name;
-  size_t rows = 0, cols = 0;  // cols 0 = vector of `rows`
-  size_t off = 0;             // element offset in the blob
-  int kind = 0;               // synthetic fill: 0 matrix (uniform, variance 1/cols), 1 norm weight (about 1), 2 small vector
-  size_t elems() const { return rows * (cols ? cols : 1); }
-};
-
-bool read_file(const std::string& path, std::string* out) {
-  FILE* f = fopen(path.c_str(), "rb");
-  if (!f) return false;
-  fseek(f, 0, SEEK_END);
-  const long n = ftell(f);
-  fseek(f, 0, SEEK_SET);
-  out->resize(n > 0 ? (size_t)n : 0);
-  const size_t got = n > 0 ? fread(&(*out)[0], 1, (size_t)n, f) : 0;
-  fclose(f);
-  return got == out->size();
-}
-
 #define NEED(cond, msg)      \
   do {                       \
     if (!(cond)) return msg; \
@@ -116,19 +96,9 @@ std::string parse_config(const JsonValue& root, NgModel* m) {
 
 // tensors in blob order; tensors that one GEMM reads as a single matrix are adjacent (no padding between them)
 std::vector<TensorSpec> build_layout(const NgModel& m) {
-  std::vector<TensorSpec> t;
-  size_t off = 0;
-  auto pad = [&]() { off = (off + 127) / 128 * 128; };  // 256-byte boundaries between groups
-  auto add = [&](const std::string& name, size_t rows, size_t cols, int kind) {
-    TensorSpec s;
-    s.name = name;
-    s.rows = rows;
-    s.cols = cols;
-    s.off = off;
-    s.kind = kind;
-    off += s.elems();
-    t.push_back(s);
-  };
+  BlobLayout bl;
+  auto pad = [&]() { bl.pad(); };  // 256-byte boundaries between groups
+  auto add = [&](const std::string& name, size_t rows, size_t cols, int kind) { bl.add(name, rows, cols, kind); };
   const size_t W = m.width;
   pad(), add("embed", m.vocab, W, 0);
   for (size_t i = 0; i < m.layers.size(); ++i) {
@@ -167,70 +137,11 @@ std::vector<TensorSpec> build_layout(const NgModel& m) {
   }
   pad(), add("final.norm", W, 0, 1);
   pad(), add("head", m.vocab, W, 0);
-  return t;
+  return bl.t;
 }
 
 size_t layout_elems(const std::vector<TensorSpec>& t) { return t.empty() ? 0 : t.back().off + t.back().elems(); }
 
-uint16_t f32_to_bf16_bits(float f) {
-  uint32_t u;
-  memcpy(&u, &f, 4);
-  u += 0x7fffu + ((u >> 16) & 1u);
-  return (uint16_t)(u >> 16);
-}
-
-// counter hash -> uniform in [-1, 1)
-float hash_uniform(uint64_t seed, uint64_t i) {
-  uint64_t z = seed + 0x9e3779b97f4a7c15ull * (i + 1);
-  z = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
-  z = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
-  z ^= z >> 31;
-  return (float)((double)(z >> 11) * (1.0 / 9007199254740992.0) * 2.0 - 1.0);
-}
-
-void fill_synthetic(const std::vector<TensorSpec>& t, uint64_t seed, std::vector<uint16_t>* blob) {
-  for (size_t k = 0; k < t.size(); ++k) {
-    const TensorSpec& s = t[k];
-    const float a = s.kind == 0 ? sqrtf(3.0f / (float)s.cols) : 0.f;
-    for (size_t i = 0; i < s.elems(); ++i) {
-      const float u = hash_uniform(seed + 1315423911ull * k, i);
-      const float v = s.kind == 0 ? a * u : (s.kind == 1 ? 1.0f + 0.1f * u : 0.5f * u);
-      (*blob)[s.off + i] = f32_to_bf16_bits(v);
-    }
-  }
-}
-
-std::string load_safetensors(const std::string& path, const std::vector<TensorSpec>& t, std::vector<uint16_t>* blob) {
-  FILE* f = fopen(path.c_str(), "rb");
-  if (!f) return "cannot open " + path;
-  unsigned char lenb[8];
-  if (fread(lenb, 1, 8, f) != 8) return fclose(f), "short safetensors file " + path;
-  uint64_t hl = 0;
-  for (int i = 7; i >= 0; --i) hl = (hl << 8) | lenb[i];
-  if (hl == 0 || hl > ((uint64_t)1 << 30)) return fclose(f), "bad safetensors header length in " + path;
-  std::string hdr((size_t)hl, '\0');
-  if (fread(&hdr[0], 1, (size_t)hl, f) != (size_t)hl) return fclose(f), "short safetensors header in " + path;
-  JsonValue root;
-  std::string err;
-  if (!JsonReader::parse(hdr.data(), hdr.data() + hdr.size(), &root, &err)) return fclose(f), path + ": " + err;
-  const size_t data0 = 8 + (size_t)hl;
-  for (const TensorSpec& s : t) {
-    const JsonValue* rec = root.have(s.name.c_str());
-    if (!rec) return fclose(f), "tensor " + s.name + " missing in " + path;
-    const JsonValue* dt = rec->have("dtype");
-    const JsonValue* sh = rec->have("shape");
-    const JsonValue* of = rec->have("data_offsets");
-    if (!dt || !sh || !of || of->arr.size() != 2) return fclose(f), "tensor " + s.name + ": malformed record";
-    if (dt->str != "BF16") return fclose(f), "tensor " + s.name + ": dtype " + dt->str + " (only BF16 weights are loaded)";
-    size_t n = 1;
-    for (const JsonValue& dv : sh->arr) n *= (size_t)llround(dv.num);
-    const size_t b0 = (size_t)llround(of->arr[0].num), b1 = (size_t)llround(of->arr[1].num);
-    if (n != s.elems() || b1 - b0 != 2 * n) return fclose(f), "tensor " + s.name + ": shape does not fit the configuration";
-    if (fseek(f, (long)(data0 + b0), SEEK_SET) != 0 || fread(&(*blob)[s.off], 2, n, f) != n) return fclose(f), "tensor " + s.name + ": short read";
-  }
-  fclose(f);
-  return "";
-}
 
 #define CUS(expr)                                                      \
   do {                                                                 \
@@ -382,37 +293,19 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   CUS(fbuf(&m->hs, R * w_hs));
   CUS(fbuf(&m->ys, R * W));
   CUS(fbuf(&m->xo, R * W));
-  CUS(fbuf(&m->logits, R * (size_t)m->vocab));
   m->attn_ws_floats = (size_t)4096 * (max_rank + 2);  // up to 4096 (row, head, split) partial results
   CUS(fbuf(&m->attn_ws, m->attn_ws_floats));
   if (!m->f32) {
     size_t maxk = W, maxn = std::max<size_t>(W, (size_t)m->vocab);
     maxk = std::max(maxk, std::max(w2, std::max(w3, w_hs)));
     maxn = std::max(maxn, std::max(w0, w_hs));
-    CUS(cudaMalloc(&m->ab, R * maxk * sizeof(bf16)));
-    CUS(cudaMalloc(&m->cb, R * maxn * sizeof(bf16)));
-    m->tc_ws_bytes = (size_t)64 << 20;
-    CUS(cudaMalloc(&m->tc_ws, m->tc_ws_bytes));
-    CUS(cudaMalloc(&m->tc_counters, 8192 * sizeof(int)));
-    CUS(cudaMemsetAsync(m->tc_counters, 0, 8192 * sizeof(int), e->stream));
-    m->tc_maps = new std::map<const bf16*, TensorMap2D>();
-    const char* v = getenv("QIE_NG_TC");
-    m->use_tc = !(v && v[0] == '0');
+    CUS(m->tc.alloc(R, maxk, maxn, e->stream));
   }
-  CUS(cudaMalloc(&m->logits_bf, R * (size_t)m->vocab * sizeof(bf16)));
+  CUS(m->alloc_row_buffers(R));
   CUS(cudaMalloc(&m->top_idx, R * w_top * sizeof(int)));
   CUS(cudaMalloc(&m->perm_row, R * w_top * sizeof(int)));
   CUS(cudaMalloc(&m->slot_of, R * w_top * sizeof(int)));
   CUS(cudaMalloc(&m->grp_off, ((size_t)m->max_experts + 2) * sizeof(int)));
-  CUS(cudaMalloc(&m->seg_start, (R + 1) * sizeof(int)));
-  CUS(cudaMalloc(&m->seg_slot, (R + 1) * sizeof(int)));
-  CUS(cudaMalloc(&m->out_rows, (R + 1) * sizeof(int)));
-  CUS(cudaMalloc(&m->iota, (R + 1) * sizeof(int)));
-  {
-    std::vector<int> io(R + 1);
-    for (size_t i = 0; i <= R; ++i) io[i] = (int)i;
-    CUS(cudaMemcpy(m->iota, io.data(), (R + 1) * sizeof(int), cudaMemcpyHostToDevice));
-  }
   e->logits_rows = (int)R;
   CUS(cudaStreamSynchronize(e->stream));
   return "";
@@ -424,15 +317,16 @@ std::string create_common(qie_engine* e, const std::string& cfg_text, const std:
   std::string err;
   if (!JsonReader::parse(cfg_text.data(), cfg_text.data() + cfg_text.size(), &root, &err)) return "config.json: " + err;
   e->ng = new NgModel();
+  e->fam = e->ng;
   err = parse_config(root, e->ng);
   if (!err.empty()) return err;
   const std::vector<TensorSpec> t = build_layout(*e->ng);
   std::vector<uint16_t> blob(layout_elems(t), 0);
   if (st_path) {
-    err = load_safetensors(*st_path, t, &blob);
+    err = load_safetensors_blob(*st_path, t, &blob);
     if (!err.empty()) return err;
   } else {
-    fill_synthetic(t, seed, &blob);
+    fill_synthetic_blob(t, seed, &blob);
   }
   return finish_setup(e, t, blob, code);
 }
@@ -442,7 +336,7 @@ std::string create_common(qie_engine* e, const std::string& cfg_text, const std:
 std::string nogatar_create(qie_engine* e, const std::string& dir, int* code) {
   std::string cfg;
   *code = QIE_EIO;
-  if (!read_file(dir + "/config.json", &cfg)) return "cannot read " + dir + "/config.json";
+  if (!read_text_file(dir + "/config.json", &cfg)) return "cannot read " + dir + "/config.json";
   const std::string st = dir + "/model.safetensors";
   return create_common(e, cfg, &st, 0, code);
 }
@@ -451,94 +345,28 @@ std::string nogatar_create_synthetic(qie_engine* e, const std::string& cfg_json,
   return create_common(e, cfg_json, nullptr, seed, code);
 }
 
-void nogatar_free(qie_engine* e) {
-  NgModel* m = e->ng;
-  if (!m) return;
+void NgModel::release() {
+  NgModel* m = this;
   void* dev[] = {m->blob, m->lat_pool, m->state, m->x, m->y, m->p0, m->p1, m->p2, m->p3, m->zr, m->top_w, m->he, m->ye, m->hs, m->ys, m->xo,
-                 m->logits, m->logits_bf, m->top_idx, m->perm_row, m->slot_of, m->grp_off, m->seg_start, m->seg_slot, m->out_rows, m->iota,
-                 m->layer_dump, m->attn_ws, m->ab, m->cb, m->tc_ws, m->tc_counters};
-  delete static_cast<std::map<const bf16*, TensorMap2D>*>(m->tc_maps);
+                 m->top_idx, m->perm_row, m->slot_of, m->grp_off, m->attn_ws};
+  m->tc.release();
+  m->release_row_buffers();
   for (void* p : dev)
     if (p) cudaFree(p);
   for (float* p : m->rope_cos)
     if (p) cudaFree(p);
   for (float* p : m->rope_sin)
     if (p) cudaFree(p);
-  delete m;
-  e->ng = nullptr;
 }
 
-void nogatar_reset_slot(qie_engine* e, int seq) {
-  NgModel* m = e->ng;
-  if (m && m->state) cudaMemsetAsync(m->state + (size_t)seq * m->slot_floats, 0, m->slot_floats * sizeof(float), e->stream);
+void NgModel::reset_slot(qie_engine* e, int seq) {
+  if (state) cudaMemsetAsync(state + (size_t)seq * slot_floats, 0, slot_floats * sizeof(float), e->stream);
 }
 
+#define NG_TRY FAM_TRY
 
-// C[n, N] = act(A[n, K] W[N, K]^T) on the tcgen05 GEMM: A rows -> dense bf16, result bf16 -> fp32 rows of C.
-// Used in bf16 serving precision for more than 16 rows when the shape fits the kernel's tiles; the operands and the
-// result are the same bf16 values as on the fp32-accumulate path (round_a / round_c), only the summation order differs.
-static bool tc_fits(const NgModel* m, int n, int K, int N, const bf16* W) {
-  return !m->f32 && m->use_tc && m->tc_maps && n > 16 && K >= 64 && K % 64 == 0 && N >= 128 && N % 8 == 0 &&
-         (reinterpret_cast<uintptr_t>(W) & 15) == 0;
-}
-
-static cudaError_t tc_gemm(qie_engine* e, const float* A, int lda, const bf16* W, int K, int N, float* C, int ldc, int act, int n) {
-  NgModel* m = e->ng;
-  cudaStream_t st = e->stream;
-  auto* maps = static_cast<std::map<const bf16*, TensorMap2D>*>(m->tc_maps);
-  auto it = maps->find(W);
-  if (it == maps->end()) {
-    TensorMap2D wm;
-    cudaError_t r = make_tensor_map_2d(&wm, W, N, K, 128);
-    if (r != cudaSuccess) return r;
-    it = maps->emplace(W, wm).first;
-  }
-  cudaError_t r = launch_rows_f32_to_bf16(A, lda, nullptr, m->ab, K, n, st);
-  if (r != cudaSuccess) return r;
-  TensorMap2D xmap;
-  if ((r = make_tensor_map_2d(&xmap, m->ab, n, K, tc_token_tile(n))) != cudaSuccess) return r;
-  TcGemm t{};
-  t.w[0] = &it->second;
-  t.rows[0] = N;
-  t.x = &xmap;
-  t.nseg = 1;
-  t.M = n;
-  t.K = K;
-  t.epi = EPI_STORE;
-  t.out = m->cb;
-  t.ld_out = N;
-  t.ws = m->tc_ws;
-  t.ws_bytes = m->tc_ws_bytes;
-  t.max_splits = (int)std::max<size_t>(1, m->tc_ws_bytes / ((size_t)n * N * sizeof(float)));
-  t.counters = m->tc_counters;
-  t.n_counters = 8192;
-  t.w_static = 0;  // the operand comes from the conversion kernel in front
-  int nl = 0;
-  if ((r = launch_gemm_tcgen05(t, e->num_sms, st, &nl)) != cudaSuccess) return r;
-  e->launches += nl + 1;
-  return launch_rows_bf16_to_f32(m->cb, N, C, ldc, act, n, st);
-}
-
-// launch + count + (when profiling) an event pair per launch, summed per kernel class by qie_profile_end
-#define NG_TRY(kind, expr)                                   \
-  do {                                                       \
-    qie_engine::ProfRec _r{kind, nullptr, nullptr};          \
-    if (e->prof_on) {                                        \
-      cudaEventCreate(&_r.a);                                \
-      cudaEventCreate(&_r.b);                                \
-      cudaEventRecord(_r.a, e->stream);                      \
-    }                                                        \
-    cudaError_t _e = (expr);                                 \
-    if (_e != cudaSuccess) return _e;                        \
-    if (e->prof_on) {                                        \
-      cudaEventRecord(_r.b, e->stream);                      \
-      e->prof.push_back(_r);                                 \
-    }                                                        \
-    ++e->launches;                                           \
-  } while (0)
-
-cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_kv_len, float temperature, bool advance) {
-  NgModel* m = e->ng;
+cudaError_t NgModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max_kv_len, float temperature, bool advance) {
+  NgModel* m = this;
   cudaStream_t st = e->stream;
   const int W = m->width;
   const int rnd = m->f32 ? 0 : 1;  // bf16 serving precision: operands and results of the projections are bf16 values
@@ -553,7 +381,7 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_
   };
   // plain projection: the tcgen05 GEMM when the shape and the precision allow, else the fp32-accumulate kernels
   auto proj = [&](const float* A, int lda, const bf16* Wt, int K, int N, float* C, int ldc, int act, int rows) {
-    if (tc_fits(m, rows, K, N, Wt)) return tc_gemm(e, A, lda, Wt, K, N, C, ldc, act, rows);
+    if (!m->f32 && m->tc.fits(rows, K, N, Wt)) return m->tc.gemm(e, A, lda, Wt, K, N, C, ldc, act, rows);
     GemmF32 g = gemm(A, lda, Wt, K, N, C, ldc, act, rnd);
     g.M = rows;
     return launch_gemm_f32(g, st);
@@ -646,14 +474,7 @@ cudaError_t nogatar_forward(qie_engine* e, int n, int n_seg, int n_out, int max_
     NG_TRY(KK_LM_HEAD, launch_gemm_f32(g, st));
   }
   if (m->softcap > 0.f) NG_TRY(KK_LM_HEAD, launch_softcap_f32(m->logits, (size_t)n_out * m->vocab, m->softcap, st));
-  if (e->topk <= 1) {
-    NG_TRY(KK_SAMPLE, launch_argmax_f32(m->logits, e->sampled_d, n_out, m->vocab, st));  // greedy on the fp32 logits
-  } else {  // the engine's top-k sampler reads bf16 rows
-    NG_TRY(KK_SAMPLE, launch_cast_f32_bf16(m->logits, m->logits_bf, (size_t)n_out * m->vocab, st));
-    NG_TRY(KK_SAMPLE, launch_sample_topk(m->logits_bf, e->sampled_d, n_out, m->vocab, temperature, e->topk, e->seed, 0, e->add_step ? e->rowstep_d : nullptr, st));
-  }
-  if (advance) NG_TRY(KK_ADVANCE, launch_advance(e->pos_d, e->ids_d, e->sampled_d, n_out, e->rowstep_d, st));
-  return cudaSuccess;
+  return sample_rows(e, n_out, temperature, advance);
 }
 
 }  // namespace qie

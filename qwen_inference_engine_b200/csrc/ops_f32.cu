@@ -150,7 +150,7 @@ __global__ void __launch_bounds__(256) gemm_f32_kernel(const GemmF32 g) {
       const int n = n0 + tx * 4 + j;
       if (n >= g.N) continue;
       float v = acc[i][j];
-      if (g.bias) v += bf2f(g.bias[n]);
+      if (g.bias) v += bf2f(g.bias[(size_t)z * g.bias_batch + n]);
       if (g.act == 1) {
         v = fmaxf(v, 0.f);
         v = v * v;
@@ -263,7 +263,7 @@ __global__ void __launch_bounds__(256) gemm_bf16_mma_kernel(const GemmF32 g) {
       const int m = m0 + wm + gq + (u >> 1) * 8, n = n0 + wn + j * 8 + 2 * tq + (u & 1);
       if (m >= Mz || n >= g.N) continue;
       float v = acc[j][u];
-      if (g.bias) v += bf2f(g.bias[n]);
+      if (g.bias) v += bf2f(g.bias[(size_t)z * g.bias_batch + n]);
       if (g.act == 1) {
         v = fmaxf(v, 0.f);
         v = v * v;
@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(256) gemv_f32_kernel(const GemmF32 g) {
     if (lane == 0) {
       for (int i = 0; i < mr; ++i) {
         float v = acc[i];
-        if (g.bias) v += bf2f(g.bias[n]);
+        if (g.bias) v += bf2f(g.bias[(size_t)z * g.bias_batch + n]);
         if (g.act == 1) {
           v = fmaxf(v, 0.f);
           v = v * v;

@@ -1,0 +1,272 @@
+// recurrent.cu -- the short causal convolution and the two linear recurrences of the fp32-stream families
+// (fosavik.h): the real-gated linear recurrent unit of Griffin (one state per channel) and the state-space recurrence
+// of Mamba-2 (a state matrix per head), with the gated group norm behind it and the clamped gated activation of the
+// feed-forward.  A launch walks SEGMENTS: runs of consecutive rows of one sequence, whose state lives in the
+// sequence's slot and is carried from call to call.  Everything that enters a recurrence is fp32.
+#include <algorithm>
+
+#include "fosavik.h"
+#include "launch.h"
+
+namespace qie {
+namespace {
+
+constexpr int CONV_MAX_TAPS = 8;
+constexpr int CONV_ROWS = 64;  // rows of a segment per CTA
+
+__device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
+__device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
+__device__ __forceinline__ float siluf_(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float gelu_tanhf_(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// grid (segments, channel blocks, row chunks): a thread owns a channel and walks CONV_ROWS rows of the segment with
+// the last taps-1 inputs in registers; inputs before the segment come from the slot's tail
+__global__ void __launch_bounds__(128) causal_conv_kernel(const ConvArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const int t0 = r0 + blockIdx.z * CONV_ROWS, t1 = min(r1, t0 + CONV_ROWS);
+  if (t0 >= r1 || c >= a.channels) return;
+  const int taps = a.taps;
+  const float* tail = a.tail + (size_t)a.seg_slot[seg] * a.slot_stride;
+  const float ib = a.in_bias ? bf2f(a.in_bias[c]) : 0.f;
+  float w[CONV_MAX_TAPS], win[CONV_MAX_TAPS];  // win[i]: input at t - (taps-1-i)
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) win[i] = 0.f;
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    w[i] = i < taps ? bf2f(a.w[(size_t)c * taps + i]) : 0.f;
+    if (i < taps - 1) {  // input at row t0 - (taps-1-i)
+      const int t = t0 - (taps - 1 - i);
+      win[i + 1] = t >= r0 ? a.x[(size_t)t * a.ldx + c] + ib : tail[(size_t)(taps - 1 - (r0 - t)) * a.channels + c];
+    }
+  }
+  const float bias = bf2f(a.b[c]);
+  for (int t = t0; t < t1; ++t) {
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS - 1; ++i) win[i] = win[i + 1];
+    // after the shift win[taps-1] must hold the current input: the window is kept right-aligned at index taps-1
+    const float cur = a.x[(size_t)t * a.ldx + c] + ib;
+    float acc = bias;
+#pragma unroll
+    for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+      if (i == taps - 1) win[i] = cur;
+      if (i < taps) acc = fmaf(w[i], win[i], acc);
+    }
+    a.out[(size_t)t * a.ldo + c] = a.act == 1 ? siluf_(acc) : acc;
+  }
+}
+
+// thread (segment, channel): the new tail = the last taps-1 inputs (rows of the segment, older ones from the old tail)
+__global__ void conv_tail_kernel(const ConvArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1], taps = a.taps;
+  float* tail = a.tail + (size_t)a.seg_slot[seg] * a.slot_stride;
+  const float ib = a.in_bias ? bf2f(a.in_bias[c]) : 0.f;
+  float nv[CONV_MAX_TAPS];
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i) {
+    nv[i] = 0.f;
+    if (i < taps - 1) {  // new tail[i] = input at row r1 - (taps-1) + i
+      const int t = r1 - (taps - 1) + i;
+      nv[i] = t >= r0 ? a.x[(size_t)t * a.ldx + c] + ib : tail[(size_t)(taps - 1 - (r0 - t)) * a.channels + c];
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < CONV_MAX_TAPS; ++i)
+    if (i < taps - 1) tail[(size_t)i * a.channels + c] = nv[i];
+}
+
+// thread (segment, channel) walks the segment's rows
+__global__ void __launch_bounds__(128) lru_scan_kernel(const LruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + c;
+  float S = *sp;
+  const float k = -a.decay_c * softplusf_(bf2f(a.lam[c]));
+  const float yb = a.y_bias ? bf2f(a.y_bias[c]) : 0.f;
+  for (int t = r0; t < r1; ++t) {
+    const float r = sigmoidf_(a.zr[(size_t)t * a.ldz + c]);
+    const float i = sigmoidf_(a.zi[(size_t)t * a.ldz + c]);
+    const float u = a.u[(size_t)t * a.ldu + c];
+    const float la = k * r;
+    const float av = expf(la);
+    const float mult = sqrtf(fmaxf(-expm1f(2.0f * la), 0.f));  // sqrt(1 - a^2) without cancellation near a = 1
+    S = fmaf(av, S, mult * (i * u));
+    a.out[(size_t)t * a.ldo + c] = S * gelu_tanhf_(a.yb[(size_t)t * a.ldy + c] + yb);
+  }
+  *sp = S;
+}
+
+// CTA (segment, head, column block): thread (ns, p) keeps rows ns, ns + NS, ... of column p of the head's state in
+// registers; the inputs of SSD_TOK tokens are staged in shared memory, the partial outputs of the NS row slices are
+// summed in a fixed order.
+constexpr int SSD_TOK = 8, SSD_NR = 32;
+
+__global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, int NS) {
+  extern __shared__ float sm[];
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, hd = blockIdx.y, p0 = blockIdx.z * PB;
+  const int N = a.N, P = a.P;
+  const int p = threadIdx.x % PB, ns = threadIdx.x / PB;
+  const int grp = hd / (a.heads / a.groups);
+  float* Bs = sm;                       // [SSD_TOK][N]
+  float* Cs = Bs + SSD_TOK * N;         // [SSD_TOK][N]
+  float* xs = Cs + SSD_TOK * N;         // [SSD_TOK][PB]
+  float* dts = xs + SSD_TOK * PB;       // [SSD_TOK] dt, then [SSD_TOK] decay
+  float* yp = dts + 2 * SSD_TOK;        // [SSD_TOK][NS][PB]
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const bool colok = p0 + p < P;
+  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)hd * N * P;
+  float S[SSD_NR];
+#pragma unroll
+  for (int i = 0; i < SSD_NR; ++i) {
+    const int n = ns + i * NS;
+    S[i] = (n < N && colok) ? sp[(size_t)n * P + p0 + p] : 0.f;
+  }
+  const float Dh = bf2f(a.D[hd]), Aneg = -expf(bf2f(a.A_log[hd])), dtb = bf2f(a.dt_bias[hd]);
+  const int nthr = blockDim.x;
+  for (int t0 = r0; t0 < r1; t0 += SSD_TOK) {
+    const int nt = min(SSD_TOK, r1 - t0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * N; i += nthr) {
+      const int t = i / N, n = i - t * N;
+      Bs[t * N + n] = a.B[(size_t)(t0 + t) * a.ld + grp * N + n];
+      Cs[t * N + n] = a.C[(size_t)(t0 + t) * a.ld + grp * N + n];
+    }
+    for (int i = threadIdx.x; i < nt * PB; i += nthr) {
+      const int t = i / PB, pp = i - t * PB;
+      xs[t * PB + pp] = p0 + pp < P ? a.x[(size_t)(t0 + t) * a.ld + (size_t)hd * P + p0 + pp] : 0.f;
+    }
+    if (threadIdx.x < nt) {
+      const float dt = softplusf_(a.dt_raw[(size_t)(t0 + threadIdx.x) * a.ld_dt + hd] + dtb);
+      dts[threadIdx.x] = dt;
+      dts[SSD_TOK + threadIdx.x] = expf(Aneg * dt);
+    }
+    __syncthreads();
+    for (int t = 0; t < nt; ++t) {
+      const float dt = dts[t], dec = dts[SSD_TOK + t];
+      const float dx = dt * xs[t * PB + p];
+      float y = 0.f;
+#pragma unroll
+      for (int i = 0; i < SSD_NR; ++i) {
+        const int n = ns + i * NS;
+        if (n < N) {
+          S[i] = fmaf(dec, S[i], Bs[t * N + n] * dx);
+          y = fmaf(S[i], Cs[t * N + n], y);
+        }
+      }
+      yp[(t * NS + ns) * PB + p] = y;
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < nt * PB; i += nthr) {
+      const int t = i / PB, pp = i - t * PB;
+      if (p0 + pp >= P) continue;
+      float y = 0.f;
+      for (int s = 0; s < NS; ++s) y += yp[(t * NS + s) * PB + pp];
+      a.y[(size_t)(t0 + t) * a.ldy + (size_t)hd * P + p0 + pp] = fmaf(Dh, xs[t * PB + pp], y);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < SSD_NR; ++i) {
+    const int n = ns + i * NS;
+    if (n < N && colok) sp[(size_t)n * P + p0 + p] = S[i];
+  }
+}
+
+// CTA (row, group)
+__global__ void __launch_bounds__(256) gated_group_norm_kernel(const float* __restrict__ y, int ldy, const float* __restrict__ z, int ldz,
+                                                               const bf16* __restrict__ w, float* __restrict__ out, int ldo, int gw, float eps) {
+  __shared__ float red[8];
+  pdl_wait();
+  pdl_trigger();
+  const int r = blockIdx.x, c0 = blockIdx.y * gw;
+  float sq = 0.f;
+  for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+    const float v = y[(size_t)r * ldy + c0 + i] * siluf_(z[(size_t)r * ldz + c0 + i]);
+    sq = fmaf(v, v, sq);
+  }
+  sq = warp_sum(sq);
+  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  __syncthreads();
+  float t = 0.f;
+  for (int i = 0; i < (int)(blockDim.x >> 5); ++i) t += red[i];
+  const float rstd = 1.0f / sqrtf(t / (float)gw + eps);
+  for (int i = threadIdx.x; i < gw; i += blockDim.x) {
+    const float v = y[(size_t)r * ldy + c0 + i] * siluf_(z[(size_t)r * ldz + c0 + i]);
+    out[(size_t)r * ldo + c0 + i] = v * rstd * bf2f(w[c0 + i]);
+  }
+}
+
+__global__ void clamped_glu_kernel(const float* __restrict__ gu, int ld, float* __restrict__ out, int ff, float limit, float alpha, size_t total) {
+  pdl_wait();
+  pdl_trigger();
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / ff;
+    const int c = (int)(i - r * ff);
+    const float g = fminf(gu[r * ld + c], limit);
+    const float u = fminf(fmaxf(gu[r * ld + ff + c], -limit), limit);
+    out[i] = g * sigmoidf_(alpha * g) * (u + 1.0f);
+  }
+}
+
+}  // namespace
+
+cudaError_t launch_causal_conv(const ConvArgs& a, cudaStream_t st) {
+  if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
+  if (a.taps < 1 || a.taps > CONV_MAX_TAPS) return cudaErrorInvalidValue;
+  const int cb = (a.channels + 127) / 128;
+  // the longest segment bounds the row chunks (n_rows rows at most)
+  cudaError_t r = launch_k(causal_conv_kernel, dim3(a.n_seg, cb, (a.n_rows + CONV_ROWS - 1) / CONV_ROWS), dim3(128), 0, st, a);
+  if (r != cudaSuccess || a.taps == 1) return r;
+  return launch_k(conv_tail_kernel, dim3(a.n_seg, cb), dim3(128), 0, st, a);
+}
+
+cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st) {
+  if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
+  return launch_k(lru_scan_kernel, dim3(a.n_seg, (a.channels + 127) / 128), dim3(128), 0, st, a);
+}
+
+cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st) {
+  if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
+  if (a.heads % a.groups) return cudaErrorInvalidValue;
+  int PB = std::min(a.P, 64);
+  int NS = (a.N + SSD_NR - 1) / SSD_NR;
+  while (PB * NS > 512 && PB > 8) PB /= 2;  // many state rows: fewer columns per CTA
+  // more row slices than the registers need: threads for latency hiding, up to 256 per CTA
+  while (PB * NS * 2 <= 256 && NS * 2 <= a.N) NS *= 2;
+  if (PB * NS > 512) return cudaErrorInvalidValue;  // more than 32 x 64 state rows per column
+  const size_t smem = ((size_t)2 * SSD_TOK * a.N + (size_t)SSD_TOK * PB + 2 * SSD_TOK + (size_t)SSD_TOK * NS * PB) * sizeof(float);
+  if (smem > 160 * 1024) return cudaErrorInvalidValue;
+  if (smem > 48 * 1024) {
+    cudaError_t r = cudaFuncSetAttribute(ssd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(ssd_scan_kernel, dim3(a.n_seg, a.heads, (a.P + PB - 1) / PB), dim3(PB * NS), smem, st, a, PB, NS);
+}
+
+cudaError_t launch_gated_group_norm(const float* y, int ldy, const float* z, int ldz, const bf16* w, float* out, int ldo, int width, int groups,
+                                    float eps, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  if (groups < 1 || width % groups) return cudaErrorInvalidValue;
+  return launch_k(gated_group_norm_kernel, dim3(n, groups), dim3(256), 0, st, y, ldy, z, ldz, w, out, ldo, width / groups, eps);
+}
+
+cudaError_t launch_clamped_glu(const float* gu, int ld, float* out, int ff, float limit, float alpha, int n, cudaStream_t st) {
+  if (n <= 0) return cudaSuccess;
+  const size_t total = (size_t)n * ff;
+  const int blocks = (int)std::min<size_t>((total + 255) / 256, 148 * 8);
+  return launch_k(clamped_glu_kernel, dim3(blocks), dim3(256), 0, st, gu, ld, out, ff, limit, alpha, total);
+}
+
+}  // namespace qie
