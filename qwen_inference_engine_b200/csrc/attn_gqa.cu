@@ -152,8 +152,8 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
       const float mn = fmaxf(mo, warp_max(s));
       float p = 0.f, cf = 1.f;
       if (mn > -INFINITY) {
-        cf = __expf(mo - mn);  // mo = -inf: 0
-        p = __expf(s - mn);
+        cf = expf(mo - mn);  // mo = -inf: 0
+        p = expf(s - mn);
       }
       const float ps = warp_sum(p);
       sc[qv * ATK + lane] = p;
@@ -207,17 +207,17 @@ __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, in
     const float* rec = a.ws + ((((size_t)r * a.heads + h) * maps + m) * n_splits) * (vd + 2);
     float M = a.unit_sink ? 0.f : -INFINITY;
     for (int s = 0; s < n_splits; ++s) M = fmaxf(M, rec[(size_t)s * (vd + 2)]);
-    float L = a.unit_sink ? __expf(-M) : 0.f;
+    float L = a.unit_sink ? expf(-M) : 0.f;
     for (int s = 0; s < n_splits; ++s) {
       const float ms = rec[(size_t)s * (vd + 2)];
-      const float w = ms > -INFINITY ? __expf(ms - M) : 0.f;
+      const float w = ms > -INFINITY ? expf(ms - M) : 0.f;
       wsp[m][s] = w;
       L = fmaf(rec[(size_t)s * (vd + 2) + 1], w, L);
     }
     inv_l[m] = 1.0f / L;
   }
   float gate = 1.f;
-  if (a.finish == 1) gate = 1.0f / (1.0f + __expf(-a.gate[(size_t)r * a.ldg + h]));
+  if (a.finish == 1) gate = 1.0f / (1.0f + expf(-a.gate[(size_t)r * a.ldg + h]));
   float sq = 0.f;
   for (int c = threadIdx.x; c < vd; c += blockDim.x) {
     float am[2] = {0.f, 0.f};

@@ -148,10 +148,10 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, 
       const int t = i / PB, pp = i - t * PB;
       xs[t * PB + pp] = p0 + pp < P ? a.x[(size_t)(t0 + t) * a.ld + (size_t)hd * P + p0 + pp] : 0.f;
     }
-    if (threadIdx.x < nt) {
-      const float dt = softplusf_(a.dt_raw[(size_t)(t0 + threadIdx.x) * a.ld_dt + hd] + dtb);
-      dts[threadIdx.x] = dt;
-      dts[SSD_TOK + threadIdx.x] = expf(Aneg * dt);
+    for (int i = threadIdx.x; i < nt; i += nthr) {
+      const float dt = softplusf_(a.dt_raw[(size_t)(t0 + i) * a.ld_dt + hd] + dtb);
+      dts[i] = dt;
+      dts[SSD_TOK + i] = expf(Aneg * dt);
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
