@@ -425,6 +425,40 @@ def nogatar_config(z, vocab=32000):
             "norm": {"eps": 1e-6}, "residual_mult": 0.5, "vocab": vocab, "width": z["width"]}
 
 
+def fosavik_config(z, vocab=32000):
+    """four layers in the order differential attention, window attention + linear recurrence, differential attention on
+    the first layer's keys and values, Mamba-2; dense feed-forward of the compared Qwen model's width"""
+    W = z["width"]
+    ff = {"ff": z["top"] * z["ff"] + z["sff"], "kind": "dense", "limit": 7.0}
+    diff = {"diff": 0.8, "dim": 64, "heads": W // 128, "kv_heads": 2, "scale": 0.125, "vdim": 128}
+    left = {"dim": 64, "heads": W // 64, "kv_heads": 4, "mask": {"keep_first": 4, "size": z["window"]}, "scale": 0.125, "vdim": 64}
+    par = {"left": left, "left_scale": 1.0, "right": {"blocks": 8, "conv": 4, "width": W}, "right_scale": 1.0}
+    ssm = {"conv": 4, "groups": 1, "heads": 2 * W // 64, "norm_groups": 1, "state": 128, "vdim": 64}
+    layers = [{"type": "attention", "mixer": diff, "mlp": ff}, {"type": "parallel", "mixer": par, "mlp": ff},
+              {"type": "attention", "mixer": dict(diff, kv_from=0), "mlp": ff}, {"type": "mamba2", "mixer": ssm, "mlp": None}]
+    return {"architecture": "Fosavik", "layers": layers, "max_positions": 8192, "norm": {"eps": 1e-6}, "streams": 4, "vocab": vocab, "width": W}
+
+
+def fosavik_macs_per_token(cfg):
+    """multiply-adds of the projections of one token (attention scores and scans not counted)"""
+    W, mac = cfg["width"], 0
+    for ly in cfg["layers"]:
+        mx = ly["mixer"]
+        if ly["type"] == "attention":
+            kv = 0 if mx.get("kv_from") is not None else mx["kv_heads"] * (2 * mx["dim"] + mx["vdim"])
+            mac += W * (mx["heads"] * 2 * mx["dim"] + kv) + mx["heads"] * mx["vdim"] * W
+        elif ly["type"] == "parallel":
+            lf, rt = mx["left"], mx["right"]
+            mac += W * (lf["heads"] * lf["dim"] + lf["kv_heads"] * lf["dim"] + lf["heads"] + 2 * rt["width"]) + lf["heads"] * lf["dim"] * W
+            mac += 2 * rt["width"] * (rt["width"] // rt["blocks"]) + rt["width"] * W
+        else:
+            inner = mx["heads"] * mx["vdim"]
+            mac += W * (2 * inner + 2 * mx["groups"] * mx["state"] + mx["heads"]) + inner * W
+        if ly.get("mlp"):
+            mac += 3 * W * ly["mlp"]["ff"]
+    return mac
+
+
 def run_family_compare(args):
     import numpy as np
     import torch
@@ -504,10 +538,16 @@ def run_family_compare(args):
         qcfg = q.make_config(dict(hidden=z["width"], inter=z["top"] * z["ff"] + z["sff"], layers=4, n_q=z["width"] // 128, n_kv=2,
                                   head_dim=128, vocab=vocab), context=8192)
         pages = (ctx + 64 + 15) // 16 * 9 + (T + 15) // 16 + 8
-        rec = {"nogatar": measure(lambda rows, seqs: q.Engine(config_json=ng_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
+        rec = {}
+        if args.family == "fosavik":
+            fv = fosavik_config(z, vocab)
+            fv_cfg = json.dumps(fv)
+            rec["fosavik"] = measure(lambda rows, seqs: q.Engine(config_json=fv_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
+                                                                 max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False)
+        rec.update({"nogatar": measure(lambda rows, seqs: q.Engine(config_json=ng_cfg, seed=7, dtype="bfloat16", page_size=16, max_pages=pages,
                                                               max_seqs=seqs, max_batch_tokens=rows, context=8192), vocab, False),
                "qwen_fast": measure(lambda rows, seqs: q.Engine(synthetic=qcfg, seed=7, numerics="fast", page_size=16, max_pages=pages, max_seqs=seqs,
-                                                                max_batch_tokens=rows, context=8192), vocab, True)}
+                                                                max_batch_tokens=rows, context=8192), vocab, True)})
         W, L = z["width"], 4
         # algorithmic work of one token: projections of the mixers + active experts + shared expert (+ head per output row)
         att = W * (z["heads"] * (z["dim"] + z["rot"]) + z["rank"] + z["rot"]) + z["heads"] * (z["dim"] + z["vdim"]) * z["rank"] + z["heads"] * z["vdim"] * W
@@ -517,7 +557,11 @@ def run_family_compare(args):
         hq = W
         qw_mac = L * (2 * hq * hq + 2 * hq * 2 * 128 + 3 * hq * (z["top"] * z["ff"] + z["sff"]))
         rec["macs_per_token"] = {"nogatar": ng_mac, "qwen": qw_mac}
-        for fam, mac in (("nogatar", ng_mac), ("qwen_fast", qw_mac)):
+        fams = [("nogatar", ng_mac), ("qwen_fast", qw_mac)]
+        if args.family == "fosavik":
+            rec["macs_per_token"]["fosavik"] = fosavik_macs_per_token(fv)
+            fams.append(("fosavik", rec["macs_per_token"]["fosavik"]))
+        for fam, mac in fams:
             r = rec[fam]
             r["prefill_tflops"] = 2 * mac * T / (r["prefill_ms"] / 1e3) / 1e12
             r["prefill_frac_of_tensor_peak"] = r["prefill_tflops"] / peaks["bf16_tflops_sustained"]
@@ -543,6 +587,8 @@ def main():
     ap.add_argument("--family-compare", action="store_true",
                     help="side measurement (not the contract line): prefill / decode throughput of the Nogatar family beside the "
                          "Qwen family at equal size, with per-kernel-class device times")
+    ap.add_argument("--family", default="nogatar", choices=["nogatar", "fosavik"],
+                    help="with --family-compare: which fp32-stream family is measured beside the Qwen family (fosavik also runs nogatar)")
     ap.add_argument("--family-size", default="", help="one of " + ", ".join(FAMILY_SIZES) + " (default: all)")
     ap.add_argument("--family-tokens", type=int, default=2048)
     ap.add_argument("--family-ctx", type=int, default=1024)

@@ -194,6 +194,243 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
   }
 }
 
+// ---------------------------------------------------------------------------------------------------------------
+// Prompt portions over a bf16 cache on tensor cores (mma.sync m16n8k16, fp32 accumulation): a CTA takes 64 consecutive
+// rows of one segment and one query head; each of its 4 warps owns 16 rows and walks the key blocks of 64 keys that the
+// CTA stages in shared memory once for all rows (the windows of neighbouring rows overlap almost completely).  Scores,
+// the online softmax and the accumulators stay in registers (the score accumulators are re-packed as the A operand of
+// the P V product); softmax, sink, gate and the differential finish are fp32.  Head sizes are padded with zeros to
+// DP / VP.  Two score maps run one after the other; the first map's result waits in the output rows.
+constexpr int PT_ROWS = 64, PT_KEYS = 64;
+
+__device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, uint32_t addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+
+template <int DP, int VP>
+__global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs a, const int* __restrict__ seg_start,
+                                                              const int* __restrict__ seg_slot, int n_seg) {
+  __shared__ __align__(16) bf16 Ks[PT_KEYS][DP + 8];
+  __shared__ __align__(16) bf16 Vs[PT_KEYS][VP + 8];
+  __shared__ const bf16* rowp[PT_KEYS];
+  __shared__ int tile_info[3];  // first row, rows, slot
+  pdl_wait();
+  pdl_trigger();
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  if (tid == 0) {
+    int left = blockIdx.x, found = 0;
+    for (int s = 0; s < n_seg && !found; ++s) {
+      const int r0 = seg_start[s], len = seg_start[s + 1] - r0, nt = (len + PT_ROWS - 1) / PT_ROWS;
+      if (left < nt) {
+        tile_info[0] = r0 + left * PT_ROWS;
+        tile_info[1] = min(PT_ROWS, len - left * PT_ROWS);
+        tile_info[2] = seg_slot[s];
+        found = 1;
+      }
+      left -= nt;
+    }
+    if (!found) tile_info[1] = 0;
+  }
+  __syncthreads();
+  const int row0 = tile_info[0], nrows = tile_info[1], slot = tile_info[2];
+  if (nrows <= 0) return;
+  const int h = blockIdx.y, g = h / (a.heads / a.kv_heads);
+  const int dim = a.dim, vd = a.vdim, maps = a.maps, kd = maps * dim;
+  const int pos0 = a.pos[row0];                       // rows of a segment are consecutive positions
+  const int pmax = pos0 + nrows - 1;
+  const int lo_min = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
+  const int qr = lane >> 2, qc = (lane & 3) * 2;      // this thread's rows qr, qr + 8 and column pair of every 8-block
+  const int wrow = warp * 16;
+  const bool rv0 = wrow + qr < nrows, rv1 = wrow + qr + 8 < nrows;
+  const int i0 = pos0 + wrow + qr, i1 = i0 + 8;       // positions of the thread's two rows
+  // 16-byte staging when every cache row piece starts on a 16-byte boundary
+  const bool vec = (a.c.page_elems % 8 == 0) && (a.c.layer_off % 8 == 0) && ((a.c.kw + a.c.vw) % 8 == 0) && (dim % 8 == 0) && (vd % 8 == 0) &&
+                   (a.c.kw % 8 == 0);
+  for (int mp = 0; mp < maps; ++mp) {
+    uint32_t qf[DP / 16][4];
+    {
+      const float* q0 = a.q + (size_t)(row0 + wrow + qr) * a.ldq + (size_t)h * kd + mp * dim;
+      const float* q1 = q0 + (size_t)8 * a.ldq;
+#pragma unroll
+      for (int kk = 0; kk < DP / 16; ++kk) {
+        const int c = kk * 16 + qc;
+        float v[8];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {  // columns c, c+1, c+8, c+9
+          const int cc = c + (e >> 1) * 8 + (e & 1);
+          v[e] = (rv0 && cc < dim) ? q0[cc] * a.scale : 0.f;
+          v[4 + e] = (rv1 && cc < dim) ? q1[cc] * a.scale : 0.f;
+        }
+        qf[kk][0] = pack2(f2bf(v[0]), f2bf(v[1]));
+        qf[kk][1] = pack2(f2bf(v[4]), f2bf(v[5]));
+        qf[kk][2] = pack2(f2bf(v[2]), f2bf(v[3]));
+        qf[kk][3] = pack2(f2bf(v[6]), f2bf(v[7]));
+      }
+    }
+    float o[VP / 8][4];
+#pragma unroll
+    for (int i = 0; i < VP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
+    for (int j0 = 0; j0 <= pmax; j0 += PT_KEYS) {
+      if (a.window > 0 && j0 + PT_KEYS - 1 < lo_min && j0 >= a.keep_first) continue;  // no row of the tile sees this block
+      __syncthreads();
+      if (tid < PT_KEYS) rowp[tid] = j0 + tid <= pmax ? reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, j0 + tid)) : nullptr;
+      __syncthreads();
+      if (vec) {
+        for (int i = tid; i < PT_KEYS * (DP / 8); i += 128) {
+          const int key = i / (DP / 8), c = (i % (DP / 8)) * 8;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (rowp[key] && c < dim) v = *reinterpret_cast<const uint4*>(rowp[key] + (size_t)g * kd + mp * dim + c);
+          *reinterpret_cast<uint4*>(&Ks[key][c]) = v;
+        }
+        for (int i = tid; i < PT_KEYS * (VP / 8); i += 128) {
+          const int key = i / (VP / 8), c = (i % (VP / 8)) * 8;
+          uint4 v = make_uint4(0u, 0u, 0u, 0u);
+          if (rowp[key] && c < vd) v = *reinterpret_cast<const uint4*>(rowp[key] + a.c.kw + (size_t)g * vd + c);
+          *reinterpret_cast<uint4*>(&Vs[key][c]) = v;
+        }
+      } else {
+        for (int i = tid; i < PT_KEYS * DP; i += 128) {
+          const int key = i / DP, c = i % DP;
+          Ks[key][c] = (rowp[key] && c < dim) ? rowp[key][(size_t)g * kd + mp * dim + c] : f2bf(0.f);
+        }
+        for (int i = tid; i < PT_KEYS * VP; i += 128) {
+          const int key = i / VP, c = i % VP;
+          Vs[key][c] = (rowp[key] && c < vd) ? rowp[key][a.c.kw + (size_t)g * vd + c] : f2bf(0.f);
+        }
+      }
+      __syncthreads();
+      // scores of the warp's 16 rows against the 64 keys
+      float s[PT_KEYS / 8][4];
+#pragma unroll
+      for (int nb = 0; nb < PT_KEYS / 8; ++nb) {
+        s[nb][0] = s[nb][1] = s[nb][2] = s[nb][3] = 0.f;
+#pragma unroll
+        for (int kk = 0; kk < DP / 16; ++kk) {
+          uint32_t b0, b1;
+          ldmatrix_x2(b0, b1, smem_u32(&Ks[nb * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8]));
+          mma_bf16_16816(s[nb], qf[kk], b0, b1);
+        }
+      }
+      // mask, running maximum
+      float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+      for (int nb = 0; nb < PT_KEYS / 8; ++nb)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + nb * 8 + qc + (e & 1);
+          const int i = (e >> 1) ? i1 : i0;
+          const bool ok = j <= i && (a.window <= 0 || i - j < a.window || j < a.keep_first);
+          if (!ok) s[nb][e] = -INFINITY;
+          if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
+          else mx0 = fmaxf(mx0, s[nb][e]);
+        }
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+      mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+      mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+      const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+      const float c0 = mn0 > -INFINITY ? expf(m0 - mn0) : 1.f, c1 = mn1 > -INFINITY ? expf(m1 - mn1) : 1.f;
+      m0 = mn0, m1 = mn1;
+      l0 *= c0, l1 *= c1;
+#pragma unroll
+      for (int i = 0; i < VP / 8; ++i) o[i][0] *= c0, o[i][1] *= c0, o[i][2] *= c1, o[i][3] *= c1;
+#pragma unroll
+      for (int nb = 0; nb < PT_KEYS / 8; ++nb) {
+        s[nb][0] = mn0 > -INFINITY ? expf(s[nb][0] - mn0) : 0.f;
+        s[nb][1] = mn0 > -INFINITY ? expf(s[nb][1] - mn0) : 0.f;
+        s[nb][2] = mn1 > -INFINITY ? expf(s[nb][2] - mn1) : 0.f;
+        s[nb][3] = mn1 > -INFINITY ? expf(s[nb][3] - mn1) : 0.f;
+        l0 += s[nb][0] + s[nb][1];
+        l1 += s[nb][2] + s[nb][3];
+      }
+      // O += P V, 16 keys per step
+#pragma unroll
+      for (int kb = 0; kb < PT_KEYS / 16; ++kb) {
+        uint32_t pa[4];
+        pa[0] = pack2(f2bf(s[2 * kb][0]), f2bf(s[2 * kb][1]));
+        pa[1] = pack2(f2bf(s[2 * kb][2]), f2bf(s[2 * kb][3]));
+        pa[2] = pack2(f2bf(s[2 * kb + 1][0]), f2bf(s[2 * kb + 1][1]));
+        pa[3] = pack2(f2bf(s[2 * kb + 1][2]), f2bf(s[2 * kb + 1][3]));
+#pragma unroll
+        for (int vb = 0; vb < VP / 8; ++vb) {
+          uint32_t b0, b1;
+          ldmatrix_x2_trans(b0, b1, smem_u32(&Vs[kb * 16 + (lane & 15)][vb * 8]));
+          mma_bf16_16816(o[vb], pa, b0, b1);
+        }
+      }
+    }
+    // the rows' sums over the quad, the sink, the normalisation
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    float f0, f1;
+    if (a.unit_sink) {
+      const float M0 = fmaxf(m0, 0.f), M1 = fmaxf(m1, 0.f);
+      const float e0 = m0 > -INFINITY ? expf(m0 - M0) : 0.f, e1 = m1 > -INFINITY ? expf(m1 - M1) : 0.f;
+      f0 = e0 / (l0 * e0 + expf(-M0));
+      f1 = e1 / (l1 * e1 + expf(-M1));
+    } else {
+      f0 = l0 > 0.f ? 1.0f / l0 : 0.f;
+      f1 = l1 > 0.f ? 1.0f / l1 : 0.f;
+    }
+    float* out0 = a.out + (size_t)(row0 + wrow + qr) * a.ldo + (size_t)h * vd;
+    float* out1 = out0 + (size_t)8 * a.ldo;
+    const bool last = mp == maps - 1;
+    float g0 = 1.f, g1 = 1.f;
+    if (a.finish == 1) {
+      if (rv0) g0 = 1.0f / (1.0f + expf(-a.gate[(size_t)(row0 + wrow + qr) * a.ldg + h]));
+      if (rv1) g1 = 1.0f / (1.0f + expf(-a.gate[(size_t)(row0 + wrow + qr + 8) * a.ldg + h]));
+    }
+    float sq0 = 0.f, sq1 = 0.f;
+#pragma unroll
+    for (int vb = 0; vb < VP / 8; ++vb) {
+      const int c = vb * 8 + qc;
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        if (c + e >= vd) continue;
+        float v0 = o[vb][e] * f0, v1 = o[vb][2 + e] * f1;
+        if (last && a.finish == 1) v0 *= g0, v1 *= g1;
+        if (last && a.finish == 2) {  // the first map's result was parked in the output rows by this thread
+          v0 = (rv0 ? out0[c + e] : 0.f) - a.lam * v0;
+          v1 = (rv1 ? out1[c + e] : 0.f) - a.lam * v1;
+          sq0 = fmaf(v0, v0, sq0), sq1 = fmaf(v1, v1, sq1);
+          o[vb][e] = v0, o[vb][2 + e] = v1;
+        } else {
+          if (rv0) out0[c + e] = v0;
+          if (rv1) out1[c + e] = v1;
+        }
+      }
+    }
+    if (last && a.finish == 2) {
+      sq0 += __shfl_xor_sync(0xffffffffu, sq0, 1);
+      sq0 += __shfl_xor_sync(0xffffffffu, sq0, 2);
+      sq1 += __shfl_xor_sync(0xffffffffu, sq1, 1);
+      sq1 += __shfl_xor_sync(0xffffffffu, sq1, 2);
+      const float r0 = a.post / sqrtf(sq0 / (float)vd + a.eps), r1 = a.post / sqrtf(sq1 / (float)vd + a.eps);
+#pragma unroll
+      for (int vb = 0; vb < VP / 8; ++vb) {
+        const int c = vb * 8 + qc;
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          if (c + e >= vd) continue;
+          if (rv0) out0[c + e] = o[vb][e] * r0;
+          if (rv1) out1[c + e] = o[vb][2 + e] * r1;
+        }
+      }
+    }
+  }
+}
+
+template <int DP>
+cudaError_t launch_prefill_mma_v(const GqaAttnArgs& a, const int* seg_start, const int* seg_slot, int n_seg, cudaStream_t st) {
+  const dim3 grid((a.n + PT_ROWS - 1) / PT_ROWS + n_seg, a.heads), block(128);
+  if (a.vdim <= 32) return launch_k(gqa_prefill_mma_kernel<DP, 32>, grid, block, 0, st, a, seg_start, seg_slot, n_seg);
+  if (a.vdim <= 64) return launch_k(gqa_prefill_mma_kernel<DP, 64>, grid, block, 0, st, a, seg_start, seg_slot, n_seg);
+  return launch_k(gqa_prefill_mma_kernel<DP, 128>, grid, block, 0, st, a, seg_start, seg_slot, n_seg);
+}
+
 // CTA (row, head): merges the key splits of each map, adds the sink, applies the finishing step
 __global__ void __launch_bounds__(128) gqa_finish_kernel(const GqaAttnArgs a, int n_splits) {
   extern __shared__ float o[];  // [vd]
@@ -257,6 +494,14 @@ cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches) {
   if (n_launches) *n_launches = 0;
   if (a.n <= 0) return cudaSuccess;
+  // prompt portions over a bf16 cache: the tensor-core kernel (one launch, no workspace)
+  if (a.seg_start && a.c.elt_bytes == 2 && a.n >= 64 && a.dim <= 128 && a.vdim <= 128 && a.maps <= 2 && a.heads % a.kv_heads == 0 &&
+      (a.finish != 2 || a.maps == 2)) {
+    if (n_launches) *n_launches = 1;
+    if (a.dim <= 32) return launch_prefill_mma_v<32>(a, a.seg_start, a.seg_slot, a.n_seg, st);
+    if (a.dim <= 64) return launch_prefill_mma_v<64>(a, a.seg_start, a.seg_slot, a.n_seg, st);
+    return launch_prefill_mma_v<128>(a, a.seg_start, a.seg_slot, a.n_seg, st);
+  }
   if (a.maps < 1 || a.maps > 2 || a.heads % a.kv_heads || (a.finish == 2 && a.maps != 2) || a.maps * a.vdim > ATHREADS * AMAXACC)
     return cudaErrorInvalidValue;
   const int hpg = a.heads / a.kv_heads;

@@ -101,6 +101,11 @@ struct GqaAttnArgs {
   float* ws = nullptr;
   size_t ws_floats = 0;
   int num_sms = 148;
+  // segments of the batch (runs of consecutive rows of one sequence, [n_seg + 1] row bounds and [n_seg] slots): with
+  // them, 64 rows or more and a bf16 cache the rows run 64 at a time on tensor cores
+  const int* seg_start = nullptr;
+  const int* seg_slot = nullptr;
+  int n_seg = 0;
 };
 // floats of workspace that n rows need with one split
 inline size_t gqa_ws_floats(int n, int heads, int maps, int vdim) { return (size_t)n * heads * maps * (vdim + 2); }

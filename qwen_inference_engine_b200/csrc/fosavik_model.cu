@@ -425,6 +425,7 @@ cudaError_t FvModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       g.window = A.window, g.keep_first = A.keep_first, g.eps = m->eps;
       g.pos = e->pos_d, g.slot = e->slot_d, g.block_table = e->block_table_d, g.max_pages = e->max_pages_per_seq, g.n = n, g.max_keys = max_kv_len;
       g.ws = m->attn_ws, g.ws_floats = m->attn_ws_floats, g.num_sms = e->num_sms;
+      g.seg_start = segs, g.seg_slot = seg_sl, g.n_seg = n_seg;
       int nl = 0;
       cudaError_t r = launch_gqa_attention(g, st, &nl);
       e->launches += nl > 0 ? nl - 1 : 0;

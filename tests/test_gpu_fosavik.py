@@ -285,6 +285,32 @@ def test_greedy_generation_through_engine_and_scheduler(tmp_path):
         eng.close()
 
 
+def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
+    # portions of 64 rows and more over the bf16 cache run 64 rows at a time on tensor cores: window and kept-token
+    # edges that fall inside a 64-key block, a sink, two sequences of unequal length in one batch, head sizes that are
+    # padded (24 -> 32).  The tolerance is bf16's; the faults it guards against are shown to be far larger.
+    layer = U.parallel_layer(heads=4, kv_heads=2, dim=24, window=37, keep_first=5, scale=0.6, width=16, blocks=2, conv=2, left_scale=1.0,
+                             right_scale=0.05)
+    cfg = U.make_config([layer, U.diff_layer(heads=2, kv_heads=1, dim=24, vdim=40, scale=0.5, diff=0.3)], width=32, vocab=29, streams=2)
+    w = U.random_weights(cfg, seed=31, gain=2.0)
+    reqs = [_tokens(cfg, 150, 4), _tokens(cfg, 81, 5)]
+    right = [_oracle_logits(cfg, w, t) for t in reqs]
+    tol = 3e-2
+    for key, val in (("size", 38), ("size", 36), ("keep_first", 6), ("keep_first", 4)):
+        bad = copy.deepcopy(cfg)
+        bad["layers"][0]["mixer"]["left"]["mask"][key] = val
+        assert np.median(_row_errors(_oracle_logits(bad, w, reqs[0])[60:], right[0][60:])) > 5 * tol, (key, val)
+    eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=32, rows=256)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    lg = eng.forward_batch([(a, reqs[0][:100]), (b, reqs[1])], range(181))  # 100 + 81 rows: four tiles, two of them ragged
+    lg2 = eng.forward_batch([(a, reqs[0][100:])], range(50))                 # below 64 rows: the per-row kernel over the same cache
+    eng.close()
+    got = [np.concatenate([lg[:100], lg2]), lg[100:]]
+    for g, r in zip(got, right):
+        err = _row_errors(g, r)
+        assert np.median(err) < tol and err.max() < 5 * tol
+
+
 def test_bf16_serving_precision(tmp_path):
     # bf16 products (tensor-core projections for portions above 16 rows), bf16 cache rows; the stream, softmax, norms and
     # recurrences stay fp32, so logits stay close to the float64 restatement and cutting changes them by rounding only
