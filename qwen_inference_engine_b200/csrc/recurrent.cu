@@ -123,6 +123,8 @@ __global__ void __launch_bounds__(128) lru_scan_kernel(const LruArgs a) {
 // summed in a fixed order.
 constexpr int SSD_TOK = 8, SSD_NR = 32;
 
+// NR state rows per thread; EXACT: N == NR * NS, so no row needs a bound check (the loop bodies stay branch-free)
+template <int NR, bool EXACT>
 __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, int NS) {
   extern __shared__ float sm[];
   pdl_wait();
@@ -139,11 +141,11 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, 
   const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
   const bool colok = p0 + p < P;
   float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)hd * N * P;
-  float S[SSD_NR];
+  float S[NR];
 #pragma unroll
-  for (int i = 0; i < SSD_NR; ++i) {
+  for (int i = 0; i < NR; ++i) {
     const int n = ns + i * NS;
-    S[i] = (n < N && colok) ? sp[(size_t)n * P + p0 + p] : 0.f;
+    S[i] = ((EXACT || n < N) && colok) ? sp[(size_t)n * P + p0 + p] : 0.f;
   }
   const float Dh = bf2f(a.D[hd]), Aneg = -expf(bf2f(a.A_log[hd])), dtb = bf2f(a.dt_bias[hd]);
   const int nthr = blockDim.x;
@@ -170,9 +172,9 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, 
       const float dx = dt * xs[t * PB + p];
       float y = 0.f;
 #pragma unroll
-      for (int i = 0; i < SSD_NR; ++i) {
+      for (int i = 0; i < NR; ++i) {
         const int n = ns + i * NS;
-        if (n < N) {
+        if (EXACT || n < N) {
           S[i] = fmaf(dec, S[i], Bs[t * N + n] * dx);
           y = fmaf(S[i], Cs[t * N + n], y);
         }
@@ -189,9 +191,9 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, 
     }
   }
 #pragma unroll
-  for (int i = 0; i < SSD_NR; ++i) {
+  for (int i = 0; i < NR; ++i) {
     const int n = ns + i * NS;
-    if (n < N && colok) sp[(size_t)n * P + p0 + p] = S[i];
+    if ((EXACT || n < N) && colok) sp[(size_t)n * P + p0 + p] = S[i];
   }
 }
 
@@ -251,19 +253,33 @@ cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st) {
 cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st) {
   if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
   if (a.heads % a.groups) return cudaErrorInvalidValue;
-  int PB = std::min(a.P, 64);
-  int NS = (a.N + SSD_NR - 1) / SSD_NR;
-  while (PB * NS > 512 && PB > 8) PB /= 2;  // many state rows: fewer columns per CTA
-  // more row slices than the registers need: threads for latency hiding, up to 256 per CTA
-  while (PB * NS * 2 <= 256 && NS * 2 <= a.N) NS *= 2;
-  if (PB * NS > 512) return cudaErrorInvalidValue;  // more than 32 x 64 state rows per column
+  // state rows per thread: the smallest of 4 / 8 / 16 / 32 that divides N (branch-free loops, many threads per column),
+  // else 32 with bound checks; the CTA's ~256 threads are NS row slices x PB columns
+  int NR = 0;
+  for (int c : {4, 8, 16, 32})
+    if (!NR && a.N % c == 0 && a.N / c <= 64) NR = c;
+  const bool exact = NR != 0;
+  if (!exact) NR = SSD_NR;
+  const int NS = (a.N + NR - 1) / NR;
+  if (NS > 64) return cudaErrorInvalidValue;  // more than 32 x 64 state rows per column
+  int PB = std::max(1, std::min(a.P, std::max(4, 256 / NS)));
   const size_t smem = ((size_t)2 * SSD_TOK * a.N + (size_t)SSD_TOK * PB + 2 * SSD_TOK + (size_t)SSD_TOK * NS * PB) * sizeof(float);
   if (smem > 160 * 1024) return cudaErrorInvalidValue;
-  if (smem > 48 * 1024) {
-    cudaError_t r = cudaFuncSetAttribute(ssd_scan_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
-    if (r != cudaSuccess) return r;
+  const dim3 grid(a.n_seg, a.heads, (a.P + PB - 1) / PB), block(PB * NS);
+  auto go = [&](auto kern) {
+    if (smem > 48 * 1024) {
+      cudaError_t r = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
+      if (r != cudaSuccess) return r;
+    }
+    return launch_k(kern, grid, block, smem, st, a, PB, NS);
+  };
+  if (!exact) return go(ssd_scan_kernel<SSD_NR, false>);
+  switch (NR) {
+    case 4: return go(ssd_scan_kernel<4, true>);
+    case 8: return go(ssd_scan_kernel<8, true>);
+    case 16: return go(ssd_scan_kernel<16, true>);
+    default: return go(ssd_scan_kernel<32, true>);
   }
-  return launch_k(ssd_scan_kernel, dim3(a.n_seg, a.heads, (a.P + PB - 1) / PB), dim3(PB * NS), smem, st, a, PB, NS);
 }
 
 cudaError_t launch_gated_group_norm(const float* y, int ldy, const float* z, int ldz, const bf16* w, float* out, int ldo, int width, int groups,

@@ -299,7 +299,7 @@ def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
     for key, val in (("size", 38), ("size", 36), ("keep_first", 6), ("keep_first", 4)):
         bad = copy.deepcopy(cfg)
         bad["layers"][0]["mixer"]["left"]["mask"][key] = val
-        assert np.median(_row_errors(_oracle_logits(bad, w, reqs[0])[60:], right[0][60:])) > 5 * tol, (key, val)
+        assert np.quantile(_row_errors(_oracle_logits(bad, w, reqs[0])[60:], right[0][60:]), 0.9) > 8 * tol, (key, val)
     eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=32, rows=256)
     a, b = eng.new_sequence(), eng.new_sequence()
     lg = eng.forward_batch([(a, reqs[0][:100]), (b, reqs[1])], range(181))  # 100 + 81 rows: four tiles, two of them ragged
@@ -308,7 +308,7 @@ def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
     got = [np.concatenate([lg[:100], lg2]), lg[100:]]
     for g, r in zip(got, right):
         err = _row_errors(g, r)
-        assert np.median(err) < tol and err.max() < 5 * tol
+        assert np.median(err) < tol and np.quantile(err, 0.9) < 2.5 * tol, (np.median(err), np.quantile(err, 0.9))
 
 
 def test_bf16_serving_precision(tmp_path):
