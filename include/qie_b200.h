@@ -181,7 +181,7 @@ typedef struct {
   int numerics;          /* QIE_NUMERICS_REFERENCE_ORDER (default) or QIE_NUMERICS_FAST */
   int semantics;         /* QIE_SEMANTICS_REFERENCE (default) or QIE_SEMANTICS_HF */
   float rms_eps;         /* RMSNorm / q,k-norm epsilon; 0 = by semantics (1e-4 reference, 1e-6 HF) */
-  int compute_dtype;     /* QIE_DTYPE_BF16 (default) or QIE_DTYPE_F32 (families with an fp32 path: Nogatar) */
+  int compute_dtype;     /* QIE_DTYPE_BF16 (default) or QIE_DTYPE_F32 (families with an fp32 path: Nogatar, Fosavik) */
 } qie_engine_opts;
 
 /* BF16: matrix products take bf16 operands with fp32 accumulation, caches hold bf16 rows; what a family defines as fp32
@@ -247,10 +247,11 @@ void qie_engine_destroy(qie_engine* e);
 
 /* Model registry: a model folder holds config.json and model.safetensors; the family is chosen by the configuration's
  * "architecture" (or the first entry of Hugging Face's "architectures").  Registered: "Nogatar" (latent attention /
- * mLSTM / mixture-of-experts decoder, loaded straight from the safetensors file) and "Qwen2ForCausalLM" /
+ * mLSTM / mixture-of-experts decoder, loaded straight from the safetensors file), "Fosavik" (hyper-connection streams;
+ * differential attention, window attention beside an RG-LRU recurrence, Mamba-2; same loader) and "Qwen2ForCausalLM" /
  * "Qwen3ForCausalLM" (converted to the blob format in a temporary folder, HF semantics).  qie_model_families returns
  * the registered architecture names separated by commas; qie_engine_family the name of an engine's family
- * ("qwen" / "nogatar"). */
+ * ("qwen" / "nogatar" / "fosavik"). */
 int qie_engine_create_from_dir(const char* model_dir, const qie_engine_opts* opts, qie_engine** out);
 /* The same family over generated weights (measurement, tests): config_json is the text of a config.json. */
 int qie_engine_create_synthetic_json(const char* config_json, uint64_t seed, const qie_engine_opts* opts, qie_engine** out);

@@ -103,6 +103,8 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
   for (int i = 0; i < AMAXACC; ++i) acc[i] = 0.f;
   const int nacc = QV * vd;
   const size_t koff = (size_t)g * kd, voff = (size_t)a.c.kw + (size_t)g * vd;
+  const bool vec8 = a.c.elt_bytes == 2 && (a.c.page_elems % 8 == 0) && (a.c.layer_off % 8 == 0) && ((a.c.kw + a.c.vw) % 8 == 0) && (kd % 8 == 0) &&
+                    (vd % 8 == 0) && (a.c.kw % 8 == 0);
   for (int t0 = i0; t0 < i1; t0 += ATK) {
     const int nk = min(ATK, i1 - t0);
     __syncthreads();  // the previous tile is consumed; q and m/l are written
@@ -120,6 +122,20 @@ __global__ void __launch_bounds__(ATHREADS) gqa_attention_kernel(const GqaAttnAr
       for (int i = tid; i < nk * vd; i += ATHREADS) {
         const int key = i / vd, c = i - key * vd;
         Vt[key * vd + c] = reinterpret_cast<const float*>(rowp[key])[voff + c];
+      }
+    } else if (vec8) {  // bf16 rows whose pieces start on 16-byte boundaries: 8 elements per load
+      const int kd8 = kd >> 3, vd8 = vd >> 3;
+      for (int i = tid; i < nk * kd8; i += ATHREADS) {
+        const int key = i / kd8, c = (i - key * kd8) * 8;
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(rowp[key]) + koff + c);
+        float* d = Kt + key * (kd + 1) + c;
+        d[0] = lo2f(v.x), d[1] = hi2f(v.x), d[2] = lo2f(v.y), d[3] = hi2f(v.y), d[4] = lo2f(v.z), d[5] = hi2f(v.z), d[6] = lo2f(v.w), d[7] = hi2f(v.w);
+      }
+      for (int i = tid; i < nk * vd8; i += ATHREADS) {
+        const int key = i / vd8, c = (i - key * vd8) * 8;
+        const uint4 v = *reinterpret_cast<const uint4*>(reinterpret_cast<const bf16*>(rowp[key]) + voff + c);
+        float* d = Vt + key * vd + c;
+        d[0] = lo2f(v.x), d[1] = hi2f(v.x), d[2] = lo2f(v.y), d[3] = hi2f(v.y), d[4] = lo2f(v.z), d[5] = hi2f(v.z), d[6] = lo2f(v.w), d[7] = hi2f(v.w);
       }
     } else {
       for (int i = tid; i < nk * kd; i += ATHREADS) {
@@ -210,9 +226,11 @@ __device__ __forceinline__ void ldmatrix_x2_trans(uint32_t& r0, uint32_t& r1, ui
 template <int DP, int VP>
 __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs a, const int* __restrict__ seg_start,
                                                               const int* __restrict__ seg_slot, int n_seg) {
-  __shared__ __align__(16) bf16 Ks[PT_KEYS][DP + 8];
-  __shared__ __align__(16) bf16 Vs[PT_KEYS][VP + 8];
-  __shared__ const bf16* rowp[PT_KEYS];
+  extern __shared__ __align__(16) unsigned char pt_smem[];  // two stages of a key block: K [2][64][DP + 8], V [2][64][VP + 8]
+  typedef bf16 KTile[PT_KEYS][DP + 8];
+  typedef bf16 VTile[PT_KEYS][VP + 8];
+  KTile* Ks = reinterpret_cast<KTile*>(pt_smem);
+  VTile* Vs = reinterpret_cast<VTile*>(pt_smem + 2 * sizeof(KTile));
   __shared__ int tile_info[3];  // first row, rows, slot
   pdl_wait();
   pdl_trigger();
@@ -271,33 +289,50 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
 #pragma unroll
     for (int i = 0; i < VP / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.f, l1 = 0.f;
-    for (int j0 = 0; j0 <= pmax; j0 += PT_KEYS) {
-      if (a.window > 0 && j0 + PT_KEYS - 1 < lo_min && j0 >= a.keep_first) continue;  // no row of the tile sees this block
-      __syncthreads();
-      if (tid < PT_KEYS) rowp[tid] = j0 + tid <= pmax ? reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, j0 + tid)) : nullptr;
-      __syncthreads();
-      if (vec) {
-        for (int i = tid; i < PT_KEYS * (DP / 8); i += 128) {
-          const int key = i / (DP / 8), c = (i % (DP / 8)) * 8;
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (rowp[key] && c < dim) v = *reinterpret_cast<const uint4*>(rowp[key] + (size_t)g * kd + mp * dim + c);
-          *reinterpret_cast<uint4*>(&Ks[key][c]) = v;
+    // key blocks that some row of the tile sees: the blocks of the kept first tokens, then from the window's lower edge on
+    auto skipped = [&](int j) { return a.window > 0 && j + PT_KEYS - 1 < lo_min && j >= a.keep_first; };
+    auto next_block = [&](int j) {
+      j += PT_KEYS;
+      return skipped(j) ? lo_min / PT_KEYS * PT_KEYS : j;
+    };
+    // a key block -> stage `buf` (cp.async when every piece of a cache row starts on a 16-byte boundary); one commit group
+    auto stage = [&](int jb, int buf) {
+      for (int i = tid; i < PT_KEYS * (DP / 8); i += 128) {
+        const int key = i / (DP / 8), c = (i % (DP / 8)) * 8;
+        bf16* dst = &Ks[buf][key][c];
+        if (jb + key <= pmax && c < dim) {
+          const bf16* src = reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + key)) + (size_t)g * kd + mp * dim + c;
+          if (vec) cp_async16(smem_u32(dst), src);
+          else
+            for (int e = 0; e < 8; ++e) dst[e] = c + e < dim ? src[e] : f2bf(0.f);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
         }
-        for (int i = tid; i < PT_KEYS * (VP / 8); i += 128) {
-          const int key = i / (VP / 8), c = (i % (VP / 8)) * 8;
-          uint4 v = make_uint4(0u, 0u, 0u, 0u);
-          if (rowp[key] && c < vd) v = *reinterpret_cast<const uint4*>(rowp[key] + a.c.kw + (size_t)g * vd + c);
-          *reinterpret_cast<uint4*>(&Vs[key][c]) = v;
+      }
+      for (int i = tid; i < PT_KEYS * (VP / 8); i += 128) {
+        const int key = i / (VP / 8), c = (i % (VP / 8)) * 8;
+        bf16* dst = &Vs[buf][key][c];
+        if (jb + key <= pmax && c < vd) {
+          const bf16* src = reinterpret_cast<const bf16*>(kv_row_ptr(a.c, a.block_table, a.max_pages, slot, jb + key)) + a.c.kw + (size_t)g * vd + c;
+          if (vec) cp_async16(smem_u32(dst), src);
+          else
+            for (int e = 0; e < 8; ++e) dst[e] = c + e < vd ? src[e] : f2bf(0.f);
+        } else {
+          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
         }
+      }
+      cp_async_commit();
+    };
+    int j0 = skipped(0) ? lo_min / PT_KEYS * PT_KEYS : 0, buf = 0;
+    stage(j0, 0);
+    while (true) {
+      const int jn = next_block(j0);
+      const bool more = jn <= pmax;
+      if (more) {  // the next block streams in while this one is multiplied
+        stage(jn, buf ^ 1);
+        cp_async_wait<1>();
       } else {
-        for (int i = tid; i < PT_KEYS * DP; i += 128) {
-          const int key = i / DP, c = i % DP;
-          Ks[key][c] = (rowp[key] && c < dim) ? rowp[key][(size_t)g * kd + mp * dim + c] : f2bf(0.f);
-        }
-        for (int i = tid; i < PT_KEYS * VP; i += 128) {
-          const int key = i / VP, c = i % VP;
-          Vs[key][c] = (rowp[key] && c < vd) ? rowp[key][a.c.kw + (size_t)g * vd + c] : f2bf(0.f);
-        }
+        cp_async_wait<0>();
       }
       __syncthreads();
       // scores of the warp's 16 rows against the 64 keys
@@ -308,7 +343,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
 #pragma unroll
         for (int kk = 0; kk < DP / 16; ++kk) {
           uint32_t b0, b1;
-          ldmatrix_x2(b0, b1, smem_u32(&Ks[nb * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8]));
+          ldmatrix_x2(b0, b1, smem_u32(&Ks[buf][nb * 8 + (lane & 7)][kk * 16 + ((lane >> 3) & 1) * 8]));
           mma_bf16_16816(s[nb], qf[kk], b0, b1);
         }
       }
@@ -355,10 +390,14 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
 #pragma unroll
         for (int vb = 0; vb < VP / 8; ++vb) {
           uint32_t b0, b1;
-          ldmatrix_x2_trans(b0, b1, smem_u32(&Vs[kb * 16 + (lane & 15)][vb * 8]));
+          ldmatrix_x2_trans(b0, b1, smem_u32(&Vs[buf][kb * 16 + (lane & 15)][vb * 8]));
           mma_bf16_16816(o[vb], pa, b0, b1);
         }
       }
+      __syncthreads();  // the stage is free for the block after the next
+      if (!more) break;
+      j0 = jn;
+      buf ^= 1;
     }
     // the rows' sums over the quad, the sink, the normalisation
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -423,12 +462,22 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
   }
 }
 
+template <int DP, int VP>
+cudaError_t launch_prefill_mma_dv(const GqaAttnArgs& a, const int* seg_start, const int* seg_slot, int n_seg, cudaStream_t st) {
+  const dim3 grid((a.n + PT_ROWS - 1) / PT_ROWS + n_seg, a.heads), block(128);
+  const size_t smem = (size_t)2 * PT_KEYS * ((DP + 8) + (VP + 8)) * sizeof(bf16);
+  if (smem > 48 * 1024) {
+    cudaError_t r = cudaFuncSetAttribute(gqa_prefill_mma_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (r != cudaSuccess) return r;
+  }
+  return launch_k(gqa_prefill_mma_kernel<DP, VP>, grid, block, smem, st, a, seg_start, seg_slot, n_seg);
+}
+
 template <int DP>
 cudaError_t launch_prefill_mma_v(const GqaAttnArgs& a, const int* seg_start, const int* seg_slot, int n_seg, cudaStream_t st) {
-  const dim3 grid((a.n + PT_ROWS - 1) / PT_ROWS + n_seg, a.heads), block(128);
-  if (a.vdim <= 32) return launch_k(gqa_prefill_mma_kernel<DP, 32>, grid, block, 0, st, a, seg_start, seg_slot, n_seg);
-  if (a.vdim <= 64) return launch_k(gqa_prefill_mma_kernel<DP, 64>, grid, block, 0, st, a, seg_start, seg_slot, n_seg);
-  return launch_k(gqa_prefill_mma_kernel<DP, 128>, grid, block, 0, st, a, seg_start, seg_slot, n_seg);
+  if (a.vdim <= 32) return launch_prefill_mma_dv<DP, 32>(a, seg_start, seg_slot, n_seg, st);
+  if (a.vdim <= 64) return launch_prefill_mma_dv<DP, 64>(a, seg_start, seg_slot, n_seg, st);
+  return launch_prefill_mma_dv<DP, 128>(a, seg_start, seg_slot, n_seg, st);
 }
 
 // CTA (row, head): merges the key splits of each map, adds the sink, applies the finishing step
