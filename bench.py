@@ -426,16 +426,16 @@ def nogatar_config(z, vocab=32000):
 
 
 def fosavik_config(z, vocab=32000):
-    """four layers in the order differential attention, window attention + linear recurrence, differential attention on
-    the first layer's keys and values, Mamba-2; dense feed-forward of the compared Qwen model's width"""
+    """four layers: differential attention, Mamba-2, window attention + linear recurrence, differential attention on the
+    first layer's keys and values (no feed-forward behind the last); dense feed-forward of the compared Qwen model's width"""
     W = z["width"]
     ff = {"ff": z["top"] * z["ff"] + z["sff"], "kind": "dense", "limit": 7.0}
     diff = {"diff": 0.8, "dim": 64, "heads": W // 128, "kv_heads": 2, "scale": 0.125, "vdim": 128}
     left = {"dim": 64, "heads": W // 64, "kv_heads": 4, "mask": {"keep_first": 4, "size": z["window"]}, "scale": 0.125, "vdim": 64}
     par = {"left": left, "left_scale": 1.0, "right": {"blocks": 8, "conv": 4, "width": W}, "right_scale": 1.0}
     ssm = {"conv": 4, "groups": 1, "heads": 2 * W // 64, "norm_groups": 1, "state": 128, "vdim": 64}
-    layers = [{"type": "attention", "mixer": diff, "mlp": ff}, {"type": "parallel", "mixer": par, "mlp": ff},
-              {"type": "attention", "mixer": dict(diff, kv_from=0), "mlp": ff}, {"type": "mamba2", "mixer": ssm, "mlp": None}]
+    layers = [{"type": "attention", "mixer": diff, "mlp": ff}, {"type": "mamba2", "mixer": ssm, "mlp": ff},
+              {"type": "parallel", "mixer": par, "mlp": ff}, {"type": "attention", "mixer": dict(diff, kv_from=0), "mlp": None}]
     return {"architecture": "Fosavik", "layers": layers, "max_positions": 8192, "norm": {"eps": 1e-6}, "streams": 4, "vocab": vocab, "width": W}
 
 

@@ -276,8 +276,8 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
 #pragma unroll
         for (int e = 0; e < 4; ++e) {  // columns c, c+1, c+8, c+9
           const int cc = c + (e >> 1) * 8 + (e & 1);
-          v[e] = (rv0 && cc < dim) ? q0[cc] * a.scale : 0.f;
-          v[4 + e] = (rv1 && cc < dim) ? q1[cc] * a.scale : 0.f;
+          v[e] = (rv0 && cc < dim) ? q0[cc] : 0.f;
+          v[4 + e] = (rv1 && cc < dim) ? q1[cc] : 0.f;
         }
         qf[kk][0] = pack2(f2bf(v[0]), f2bf(v[1]));
         qf[kk][1] = pack2(f2bf(v[4]), f2bf(v[5]));
@@ -356,7 +356,7 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
           const int j = j0 + nb * 8 + qc + (e & 1);
           const int i = (e >> 1) ? i1 : i0;
           const bool ok = j <= i && (a.window <= 0 || i - j < a.window || j < a.keep_first);
-          if (!ok) s[nb][e] = -INFINITY;
+          s[nb][e] = ok ? s[nb][e] * a.scale : -INFINITY;  // the scale meets the fp32 score, not the bf16 operand
           if (e >> 1) mx1 = fmaxf(mx1, s[nb][e]);
           else mx0 = fmaxf(mx0, s[nb][e]);
         }
@@ -379,19 +379,23 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
         l0 += s[nb][0] + s[nb][1];
         l1 += s[nb][2] + s[nb][3];
       }
-      // O += P V, 16 keys per step
+      // O += P V, 16 keys per step; the softmax weights go in as bf16 hi + lo pairs (two MMAs), so they keep ~16 bits
 #pragma unroll
       for (int kb = 0; kb < PT_KEYS / 16; ++kb) {
-        uint32_t pa[4];
-        pa[0] = pack2(f2bf(s[2 * kb][0]), f2bf(s[2 * kb][1]));
-        pa[1] = pack2(f2bf(s[2 * kb][2]), f2bf(s[2 * kb][3]));
-        pa[2] = pack2(f2bf(s[2 * kb + 1][0]), f2bf(s[2 * kb + 1][1]));
-        pa[3] = pack2(f2bf(s[2 * kb + 1][2]), f2bf(s[2 * kb + 1][3]));
+        uint32_t ph[4], pl[4];
+#pragma unroll
+        for (int f = 0; f < 4; ++f) {
+          const float x0 = s[2 * kb + (f >> 1)][(f & 1) * 2], x1 = s[2 * kb + (f >> 1)][(f & 1) * 2 + 1];
+          const bf16 h0 = f2bf(x0), h1 = f2bf(x1);
+          ph[f] = pack2(h0, h1);
+          pl[f] = pack2(f2bf(x0 - bf2f(h0)), f2bf(x1 - bf2f(h1)));
+        }
 #pragma unroll
         for (int vb = 0; vb < VP / 8; ++vb) {
           uint32_t b0, b1;
           ldmatrix_x2_trans(b0, b1, smem_u32(&Vs[buf][kb * 16 + (lane & 15)][vb * 8]));
-          mma_bf16_16816(o[vb], pa, b0, b1);
+          mma_bf16_16816(o[vb], ph, b0, b1);
+          mma_bf16_16816(o[vb], pl, b0, b1);
         }
       }
       __syncthreads();  // the stage is free for the block after the next

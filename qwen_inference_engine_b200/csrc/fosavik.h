@@ -80,7 +80,7 @@ struct KvStoreArgs {
 cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st);
 // out[r, h, :] over the keys j of row r's sequence with j <= pos and (window <= 0 or pos - j < window or j < keep_first).
 // `maps` score maps per head (queries [h][map][dim], keys [g][map][dim]) share the values [g][vdim]; head h reads kv
-// head h / (heads / kv_heads).  unit_sink adds 1 to every softmax denominator (a key of score 0 without a value).
+// head h / (heads / kv_heads).  unit_sink adds 1 to every softmax denominator (as if one more key with a zero score and nothing to contribute took part).
 // finish 0: out = a_1;  1: out = a_1 * sigmoid(gate[r, h]);  2 (maps == 2): o = a_1 - lam * a_2, out = o / sqrt(mean(o^2) + eps) * post.
 // The keys of a row may be split over CTAs; partial (max, sum, acc) go through ws and a second kernel finishes.
 struct GqaAttnArgs {

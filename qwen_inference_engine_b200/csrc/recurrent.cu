@@ -84,7 +84,8 @@ __global__ void conv_tail_kernel(const ConvArgs a) {
 }
 
 // thread (segment, channel) walks the segment's rows
-__global__ void __launch_bounds__(128) lru_scan_kernel(const LruArgs a) {
+constexpr int LRU_PF = 16;
+__global__ void __launch_bounds__(64) lru_scan_kernel(const LruArgs a) {
   pdl_wait();
   pdl_trigger();
   const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -94,10 +95,10 @@ __global__ void __launch_bounds__(128) lru_scan_kernel(const LruArgs a) {
   float S = *sp;
   const float k_ = -a.decay_c * softplusf_(bf2f(a.lam[c]));
   const float yb = a.y_bias ? bf2f(a.y_bias[c]) : 0.f;
-  for (int t0 = r0; t0 < r1; t0 += 8) {  // the loads of 8 rows are in flight together; the recurrence itself is one FMA per row
-    float zr[8], zi[8], uv[8], yv[8];
+  for (int t0 = r0; t0 < r1; t0 += LRU_PF) {  // the loads of LRU_PF rows are in flight together; the recurrence itself is one FMA per row
+    float zr[LRU_PF], zi[LRU_PF], uv[LRU_PF], yv[LRU_PF];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < LRU_PF; ++k) {
       const int t = min(t0 + k, r1 - 1);
       zr[k] = a.zr[(size_t)t * a.ldz + c];
       zi[k] = a.zi[(size_t)t * a.ldz + c];
@@ -105,7 +106,7 @@ __global__ void __launch_bounds__(128) lru_scan_kernel(const LruArgs a) {
       yv[k] = a.yb[(size_t)t * a.ldy + c];
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < LRU_PF; ++k) {
       if (t0 + k < r1) {
         const float la = k_ * sigmoidf_(zr[k]);
         const float av = expf(la);
@@ -247,7 +248,7 @@ cudaError_t launch_causal_conv(const ConvArgs& a, cudaStream_t st) {
 
 cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st) {
   if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
-  return launch_k(lru_scan_kernel, dim3(a.n_seg, (a.channels + 127) / 128), dim3(128), 0, st, a);
+  return launch_k(lru_scan_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a);
 }
 
 cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st) {

@@ -75,7 +75,7 @@ def attend(q, K, V, pos, scale, window=0, keep_first=0, unit_sink=False):
             s = (K[js, g] @ q[t, h]) * scale
             m = max(s.max(), 0.0) if unit_sink else s.max()
             e = np.exp(s - m)
-            den = e.sum() + (math.exp(-m) if unit_sink else 0.0)  # the sink: a key of score 0 without a value
+            den = e.sum() + (math.exp(-m) if unit_sink else 0.0)  # the sink: exp(0) joins the denominator and nothing joins the sum
             out[t, h] = (e / den) @ V[js, g]
     return out
 
