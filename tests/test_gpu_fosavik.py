@@ -311,6 +311,23 @@ def test_bf16_prompt_attention_on_tensor_cores_keeps_the_edges(tmp_path):
         assert np.median(err) < tol and np.quantile(err, 0.9) < 2.5 * tol, (np.median(err), np.quantile(err, 0.9))
 
 
+@pytest.mark.parametrize("dim,vdim", [(12, 20), (36, 44), (136, 132)], ids=["unaligned_small", "unaligned_padded", "beyond_tensor_core_tiles"])
+def test_bf16_prompt_attention_odd_head_sizes(tmp_path, dim, vdim):
+    # head sizes that are no multiple of 8 (cache rows without 16-byte pieces: element-wise staging) and head sizes beyond the
+    # tensor-core kernel's tiles (the per-row kernel takes the prompt); 70 rows in one portion, then single tokens
+    cfg = U.make_config([U.diff_layer(heads=2, kv_heads=1, dim=dim, vdim=vdim, scale=dim ** -0.5, diff=0.4),
+                         U.parallel_layer(heads=2, kv_heads=2, dim=dim, window=19, keep_first=2, scale=dim ** -0.5, width=12, blocks=1, conv=2)],
+                        width=40, vocab=31, streams=2)
+    w = U.random_weights(cfg, seed=37)
+    toks = _tokens(cfg, 80, 12)
+    right = _oracle_logits(cfg, w, toks)
+    eng = _engine(tmp_path, cfg, w, dtype="bfloat16", page_size=16, max_pages=16, rows=128)
+    got = _cuts(eng, toks, [70] + [1] * 10)
+    eng.close()
+    err = _row_errors(got, right)
+    assert np.median(err) < 2e-2 and np.quantile(err, 0.9) < 6e-2, (np.median(err), np.quantile(err, 0.9))
+
+
 def test_bf16_serving_precision(tmp_path):
     # bf16 products (tensor-core projections for portions above 16 rows), bf16 cache rows; the stream, softmax, norms and
     # recurrences stay fp32, so logits stay close to the float64 restatement and cutting changes them by rounding only
