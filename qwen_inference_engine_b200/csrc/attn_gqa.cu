@@ -5,6 +5,8 @@
 // the differential combination with a unit norm per head.  Softmax and accumulation are fp32; the cache rows are fp32
 // or bf16.  Keys are ALWAYS read from the cache (a row's own position is stored first), so a result does not depend
 // on how a prompt was cut or what else is in the batch.
+#include <stdlib.h>
+
 #include <algorithm>
 
 #include "fosavik.h"
@@ -231,29 +233,34 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
   typedef bf16 VTile[PT_KEYS][VP + 8];
   KTile* Ks = reinterpret_cast<KTile*>(pt_smem);
   VTile* Vs = reinterpret_cast<VTile*>(pt_smem + 2 * sizeof(KTile));
-  __shared__ int tile_info[3];  // first row, rows, slot
+  __shared__ int tile_info[5];  // segment's first row, its length, slot, the CTA's two tiles (-1: none)
   pdl_wait();
   pdl_trigger();
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   if (tid == 0) {
+    // a CTA takes tile p and tile nt-1-p of a segment: under a causal mask the late tiles see many key blocks and the early
+    // ones few, so every CTA gets about the same number
     int left = blockIdx.x, found = 0;
     for (int s = 0; s < n_seg && !found; ++s) {
-      const int r0 = seg_start[s], len = seg_start[s + 1] - r0, nt = (len + PT_ROWS - 1) / PT_ROWS;
-      if (left < nt) {
-        tile_info[0] = r0 + left * PT_ROWS;
-        tile_info[1] = min(PT_ROWS, len - left * PT_ROWS);
-        tile_info[2] = seg_slot[s];
+      const int r0 = seg_start[s], len = seg_start[s + 1] - r0, nt = (len + PT_ROWS - 1) / PT_ROWS, np = (nt + 1) / 2;
+      if (left < np) {
+        tile_info[0] = r0, tile_info[1] = len, tile_info[2] = seg_slot[s];
+        tile_info[3] = nt - 1 - left;
+        tile_info[4] = left != nt - 1 - left ? left : -1;
         found = 1;
       }
-      left -= nt;
+      left -= np;
     }
-    if (!found) tile_info[1] = 0;
+    if (!found) tile_info[3] = tile_info[4] = -1;
   }
   __syncthreads();
-  const int row0 = tile_info[0], nrows = tile_info[1], slot = tile_info[2];
-  if (nrows <= 0) return;
+  const int slot = tile_info[2];
   const int h = blockIdx.y, g = h / (a.heads / a.kv_heads);
   const int dim = a.dim, vd = a.vdim, maps = a.maps, kd = maps * dim;
+  for (int which = 0; which < 2; ++which) {
+  const int tile = tile_info[3 + which];
+  if (tile < 0) break;
+  const int row0 = tile_info[0] + tile * PT_ROWS, nrows = min(PT_ROWS, tile_info[1] - tile * PT_ROWS);
   const int pos0 = a.pos[row0];                       // rows of a segment are consecutive positions
   const int pmax = pos0 + nrows - 1;
   const int lo_min = a.window > 0 ? max(0, pos0 - a.window + 1) : 0;
@@ -464,11 +471,12 @@ __global__ void __launch_bounds__(128) gqa_prefill_mma_kernel(const GqaAttnArgs 
       }
     }
   }
+  }
 }
 
 template <int DP, int VP>
 cudaError_t launch_prefill_mma_dv(const GqaAttnArgs& a, const int* seg_start, const int* seg_slot, int n_seg, cudaStream_t st) {
-  const dim3 grid((a.n + PT_ROWS - 1) / PT_ROWS + n_seg, a.heads), block(128);
+  const dim3 grid((a.n + 2 * PT_ROWS - 1) / (2 * PT_ROWS) + n_seg, a.heads), block(128);  // upper bound of the tile pairs
   const size_t smem = (size_t)2 * PT_KEYS * ((DP + 8) + (VP + 8)) * sizeof(bf16);
   if (smem > 48 * 1024) {
     cudaError_t r = cudaFuncSetAttribute(gqa_prefill_mma_kernel<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -547,8 +555,9 @@ cudaError_t launch_kv_store_rows(const KvStoreArgs& a, cudaStream_t st) {
 cudaError_t launch_gqa_attention(const GqaAttnArgs& a, cudaStream_t st, int* n_launches) {
   if (n_launches) *n_launches = 0;
   if (a.n <= 0) return cudaSuccess;
-  // prompt portions over a bf16 cache: the tensor-core kernel (one launch, no workspace)
-  if (a.seg_start && a.c.elt_bytes == 2 && a.n >= 64 && a.dim <= 128 && a.vdim <= 128 && a.maps <= 2 && a.heads % a.kv_heads == 0 &&
+  // prompt portions over a bf16 cache: the tensor-core kernel (one launch, no workspace); QIE_ATTN_MMA=0 keeps the per-row kernel (A/B)
+  static const bool mma_on = [] { const char* v = getenv("QIE_ATTN_MMA"); return !(v && v[0] == '0'); }();
+  if (mma_on && a.seg_start && a.c.elt_bytes == 2 && a.n >= 64 && a.dim <= 128 && a.vdim <= 128 && a.maps <= 2 && a.heads % a.kv_heads == 0 &&
       (a.finish != 2 || a.maps == 2)) {
     if (n_launches) *n_launches = 1;
     if (a.dim <= 32) return launch_prefill_mma_v<32>(a, a.seg_start, a.seg_slot, a.n_seg, st);
