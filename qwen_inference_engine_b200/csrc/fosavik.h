@@ -137,7 +137,7 @@ cudaError_t launch_causal_conv(const ConvArgs& a, cudaStream_t st);
 //   r = sigmoid(zr), i = sigmoid(zi), a = exp(-decay_c * r * softplus(lam[c])), S = a S + sqrt(1 - a^2) * i * u,
 //   out = S * gelu_tanh(yb[t, c] + y_bias[c]).   state of slot s: [channels] fp32 at state + s * slot_stride.
 struct LruArgs {
-  const float* zr = nullptr;  // [n, channels] gate pre-activations (bias added)
+  const float* zr = nullptr;  // [n, channels] gate pre-activations (bias added); overwritten when the chunked form runs
   const float* zi = nullptr;
   int ldz = 0;
   const float* u = nullptr;
@@ -155,6 +155,10 @@ struct LruArgs {
   const int* seg_start = nullptr;
   const int* seg_slot = nullptr;
   int n_seg = 0, n_rows = 0;
+  // optional workspace of (n_rows / 64 + n_seg + 2) * 2 * channels floats: with it, portions of 256 rows and more in at
+  // most 64 segments run chunk-parallel (local scans, a carry pass, an apply pass)
+  float* ws = nullptr;
+  size_t ws_floats = 0;
 };
 cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st);
 // State-space recurrence per head (state S [N, P] fp32 per head and slot):
@@ -242,6 +246,8 @@ struct FvModel : RowFamily {
   TcProjector tc;
   float* attn_ws = nullptr;
   size_t attn_ws_floats = 0;
+  float* scan_ws = nullptr;  // chunk summaries of the chunk-parallel linear recurrence
+  size_t scan_ws_floats = 0;
 };
 
 std::string fosavik_create(qie_engine* e, const std::string& dir, int* code);

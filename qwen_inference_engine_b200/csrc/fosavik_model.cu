@@ -329,6 +329,8 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   CUS(fbuf(&m->xo, R * W));
   m->attn_ws_floats = (R + 2048) * hmv;  // room for key splits when a step has few rows
   CUS(fbuf(&m->attn_ws, m->attn_ws_floats));
+  m->scan_ws_floats = w2 > 1 ? (R / 64 + 64 + 2) * 2 * w2 : 0;
+  CUS(fbuf(&m->scan_ws, m->scan_ws_floats));
   if (!m->f32) CUS(m->tc.alloc(R, maxk, std::max<size_t>(std::max<size_t>(W, (size_t)m->vocab), w0), e->stream));
   CUS(m->alloc_row_buffers(R));
   e->logits_rows = (int)R;
@@ -371,7 +373,7 @@ std::string fosavik_create_synthetic(qie_engine* e, const std::string& cfg_json,
 }
 
 void FvModel::release() {
-  void* dev[] = {blob, kv_pool, state, X, hn, y, y2, p0, p1, p2, p3, xo, attn_ws};
+  void* dev[] = {blob, kv_pool, state, X, hn, y, y2, p0, p1, p2, p3, xo, attn_ws, scan_ws};
   tc.release();
   release_row_buffers();
   for (void* p : dev)
@@ -484,6 +486,7 @@ cudaError_t FvModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
         s.zr = m->p3, s.zi = m->p3 + R, s.ldz = 2 * R, s.u = m->p2, s.ldu = R, s.yb = m->p0 + oy, s.ldy = Nin, s.y_bias = L.y_b, s.lam = L.lam_w;
         s.decay_c = 8.0f, s.channels = R, s.out = m->p2, s.ldo = R, s.state = state, s.slot_stride = m->slot_floats;
         s.seg_start = segs, s.seg_slot = seg_sl, s.n_seg = n_seg, s.n_rows = n;
+        s.ws = m->scan_ws, s.ws_floats = m->scan_ws_floats;
         FAM_TRY(KK_LRU_SCAN, launch_lru_scan(s, st));
         FAM_TRY(KK_F32_PROJ, proj(m->p2, R, L.wo2, R, W, m->y2, W, n));
       }

@@ -13,6 +13,7 @@ namespace {
 
 constexpr int CONV_MAX_TAPS = 8;
 constexpr int CONV_ROWS = 64;  // rows of a segment per CTA
+constexpr int LRU_PF = 16;     // rows whose loads a scan thread keeps in flight
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
 __device__ __forceinline__ float softplusf_(float z) { return z > 20.f ? z : log1pf(expf(z)); }
@@ -84,7 +85,6 @@ __global__ void conv_tail_kernel(const ConvArgs a) {
 }
 
 // thread (segment, channel) walks the segment's rows
-constexpr int LRU_PF = 16;
 __global__ void __launch_bounds__(64) lru_scan_kernel(const LruArgs a) {
   pdl_wait();
   pdl_trigger();
@@ -117,6 +117,83 @@ __global__ void __launch_bounds__(64) lru_scan_kernel(const LruArgs a) {
     }
   }
   *sp = S;
+}
+
+// The same recurrence for long segments in three parallel steps over chunks of LRU_CHUNK rows (a chunk starts at a
+// multiple of LRU_CHUNK rows from its segment's start).  (1) every chunk runs from a zero state: the local states go to
+// `out`, the running product of the decays replaces zr, the chunk's total decay P and end state Q go to the workspace;
+// (2) one thread per channel carries the true state over the chunks (S_in of every chunk, the slot's final state);
+// (3) S_t = local_t + decay_t * S_in, times the gelu branch.  Only the rounding differs from the row-by-row kernel.
+constexpr int LRU_CHUNK = 64;
+__device__ __forceinline__ int lru_chunk_id(int r0, int seg, int k) { return r0 / LRU_CHUNK + seg + k; }  // unique over the batch
+
+__global__ void __launch_bounds__(64) lru_chunk_local_kernel(const LruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, k = blockIdx.z;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const int t0 = r0 + k * LRU_CHUNK, t1 = min(r1, t0 + LRU_CHUNK);
+  if (t0 >= r1 || c >= a.channels) return;
+  const float k_ = -a.decay_c * softplusf_(bf2f(a.lam[c]));
+  float* cum_out = const_cast<float*>(a.zr);
+  float S = 0.f, cum = 1.f;
+  for (int tb = t0; tb < t1; tb += LRU_PF) {
+    float zr[LRU_PF], zi[LRU_PF], uv[LRU_PF];
+#pragma unroll
+    for (int j = 0; j < LRU_PF; ++j) {
+      const int t = min(tb + j, t1 - 1);
+      zr[j] = a.zr[(size_t)t * a.ldz + c];
+      zi[j] = a.zi[(size_t)t * a.ldz + c];
+      uv[j] = a.u[(size_t)t * a.ldu + c];
+    }
+#pragma unroll
+    for (int j = 0; j < LRU_PF; ++j) {
+      if (tb + j < t1) {
+        const float la = k_ * sigmoidf_(zr[j]);
+        const float av = expf(la);
+        const float mult = sqrtf(fmaxf(-expm1f(2.0f * la), 0.f));
+        S = fmaf(av, S, mult * (sigmoidf_(zi[j]) * uv[j]));
+        cum *= av;
+        a.out[(size_t)(tb + j) * a.ldo + c] = S;
+        cum_out[(size_t)(tb + j) * a.ldz + c] = cum;
+      }
+    }
+  }
+  float* w = a.ws + (size_t)lru_chunk_id(r0, seg, k) * 2 * a.channels;
+  w[c] = cum;
+  w[a.channels + c] = S;
+}
+
+__global__ void __launch_bounds__(64) lru_chunk_carry_kernel(const LruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= a.channels) return;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + c;
+  float S = *sp;
+  for (int k = 0; r0 + k * LRU_CHUNK < r1; ++k) {
+    float* w = a.ws + (size_t)lru_chunk_id(r0, seg, k) * 2 * a.channels;
+    const float P = w[c], Q = w[a.channels + c];
+    w[c] = S;  // the chunk's incoming state
+    S = fmaf(P, S, Q);
+  }
+  *sp = S;
+}
+
+__global__ void __launch_bounds__(128) lru_chunk_apply_kernel(const LruArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x, k = blockIdx.z;
+  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const int t0 = r0 + k * LRU_CHUNK, t1 = min(r1, t0 + LRU_CHUNK);
+  if (t0 >= r1 || c >= a.channels) return;
+  const float Sin = a.ws[(size_t)lru_chunk_id(r0, seg, k) * 2 * a.channels + c];
+  const float yb = a.y_bias ? bf2f(a.y_bias[c]) : 0.f;
+  for (int t = t0; t < t1; ++t) {
+    const float S = fmaf(a.zr[(size_t)t * a.ldz + c], Sin, a.out[(size_t)t * a.ldo + c]);
+    a.out[(size_t)t * a.ldo + c] = S * gelu_tanhf_(a.yb[(size_t)t * a.ldy + c] + yb);
+  }
 }
 
 // CTA (segment, head, column block): thread (ns, p) keeps rows ns, ns + NS, ... of column p of the head's state in
@@ -248,6 +325,14 @@ cudaError_t launch_causal_conv(const ConvArgs& a, cudaStream_t st) {
 
 cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st) {
   if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
+  const size_t ws_need = ((size_t)a.n_rows / LRU_CHUNK + a.n_seg + 2) * 2 * a.channels;
+  if (a.ws && a.n_rows >= 4 * LRU_CHUNK && a.n_seg <= 64 && ws_need <= a.ws_floats) {  // long portions: chunks in parallel
+    const int chunks = (a.n_rows + LRU_CHUNK - 1) / LRU_CHUNK;
+    cudaError_t r = launch_k(lru_chunk_local_kernel, dim3(a.n_seg, (a.channels + 63) / 64, chunks), dim3(64), 0, st, a);
+    if (r != cudaSuccess) return r;
+    if ((r = launch_k(lru_chunk_carry_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a)) != cudaSuccess) return r;
+    return launch_k(lru_chunk_apply_kernel, dim3(a.n_seg, (a.channels + 127) / 128, chunks), dim3(128), 0, st, a);
+  }
   return launch_k(lru_scan_kernel, dim3(a.n_seg, (a.channels + 63) / 64), dim3(64), 0, st, a);
 }
 

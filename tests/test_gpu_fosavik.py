@@ -235,6 +235,29 @@ def test_far_key_among_hundreds(tmp_path):
     eng.close()
 
 
+def test_long_portions_run_the_chunked_recurrence(tmp_path):
+    # portions of 256 rows and more take the chunk-parallel form of the linear recurrence (chunks of 64 rows from the
+    # segment's start, a carry pass); two sequences in one batch, a state carried in from an earlier portion and out to
+    # decoded tokens, a decay near one (slow channels) beside fast ones
+    cfg = U.make_config([U.parallel_layer(heads=2, kv_heads=1, dim=8, window=9, keep_first=0, width=70, blocks=2, conv=3, left_scale=0.2,
+                                          right_scale=1.5, mlp=U.dense())], width=20, vocab=31, streams=2)
+    w = U.random_weights(cfg, seed=41)
+    bits, lam = w["l0.mix.right.lam"]
+    lam = lam.copy()
+    lam[:10] = -9.0  # softplus ~ 1e-4: a stays within 1e-3 of one, the state remembers hundreds of tokens
+    w["l0.mix.right.lam"] = U.bf16_round(lam.astype(np.float32))
+    reqs = [_tokens(cfg, 430, 3), _tokens(cfg, 141, 4)]
+    right = [_oracle_logits(cfg, w, t) for t in reqs]
+    eng = _engine(tmp_path, cfg, w, page_size=16, max_pages=40, rows=512)
+    a, b = eng.new_sequence(), eng.new_sequence()
+    g0 = eng.forward_batch([(a, reqs[0][:37])], range(37))                            # row by row kernel
+    g1 = eng.forward_batch([(a, reqs[0][37:337]), (b, reqs[1][:130])], range(430))    # 300 + 130 rows: chunked, ragged last chunks
+    g2 = eng.forward_batch([(a, reqs[0][337:]), (b, reqs[1][130:])], range(93 + 11))  # below 256 rows again
+    eng.close()
+    assert U.rel_err(np.concatenate([g0, g1[:300], g2[:93]]), right[0]) < TOL32
+    assert U.rel_err(np.concatenate([g1[300:], g2[93:]]), right[1]) < TOL32
+
+
 def test_first_tokens_and_long_decoding(tmp_path):
     # the first tokens (empty history: zero state, zero convolution tail, a single key) and 200 decoded tokens
     cfg = U.make_config(copy.deepcopy(MIXED[:4]), width=20, vocab=31)
