@@ -180,7 +180,15 @@ struct SsdArgs {
   const int* seg_start = nullptr;
   const int* seg_slot = nullptr;
   int n_seg = 0, n_rows = 0;
+  // optional workspace (ssd_ws_floats): with it, portions of 256 rows and more in at most 16 segments run chunk-parallel
+  float* ws = nullptr;
+  size_t ws_floats = 0;
+  float *ws_cum = nullptr, *ws_p = nullptr, *ws_state = nullptr;  // set by the launcher: parts of ws
 };
+inline size_t ssd_ws_floats(size_t rows, int heads, int N, int P) {
+  const size_t ids = rows / 64 + 16 + 2;
+  return rows * heads + ids * heads + ids * heads * (size_t)N * P;
+}
 cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st);
 // out[r, c] = v / sqrt(mean_group(v^2) + eps) * w[c] with v = y[r, c] * silu(z[r, c]); `groups` equal parts of `width`
 cudaError_t launch_gated_group_norm(const float* y, int ldy, const float* z, int ldz, const bf16* w, float* out, int ldo, int width, int groups,

@@ -330,6 +330,8 @@ std::string finish_setup(qie_engine* e, const std::vector<TensorSpec>& t, const 
   m->attn_ws_floats = (R + 2048) * hmv;  // room for key splits when a step has few rows
   CUS(fbuf(&m->attn_ws, m->attn_ws_floats));
   m->scan_ws_floats = w2 > 1 ? (R / 64 + 64 + 2) * 2 * w2 : 0;
+  for (const FvLayer& L : m->layers)
+    if (L.type == 2) m->scan_ws_floats = std::max(m->scan_ws_floats, ssd_ws_floats(R, L.m_heads, L.m_N, L.m_P));
   CUS(fbuf(&m->scan_ws, m->scan_ws_floats));
   if (!m->f32) CUS(m->tc.alloc(R, maxk, std::max<size_t>(std::max<size_t>(W, (size_t)m->vocab), w0), e->stream));
   CUS(m->alloc_row_buffers(R));
@@ -506,6 +508,7 @@ cudaError_t FvModel::forward(qie_engine* e, int n, int n_seg, int n_out, int max
       s.dt_bias = L.dt_bias, s.A_log = L.A_log, s.D = L.Dw, s.heads = L.m_heads, s.P = L.m_P, s.N = L.m_N, s.groups = L.m_groups;
       s.y = m->p2, s.ldy = inner, s.state = state, s.slot_stride = m->slot_floats;
       s.seg_start = segs, s.seg_slot = seg_sl, s.n_seg = n_seg, s.n_rows = n;
+      s.ws = m->scan_ws, s.ws_floats = m->scan_ws_floats;
       FAM_TRY(KK_SSD_SCAN, launch_ssd_scan(s, st));
       FAM_TRY(KK_F32_NORM, launch_gated_group_norm(m->p2, inner, m->p0, Nin, L.gn_w, m->p3, inner, inner, L.m_norm_groups, m->eps, n, st));
       FAM_TRY(KK_F32_PROJ, proj(m->p3, inner, L.wo, inner, W, m->y, W, n));

@@ -201,60 +201,89 @@ __global__ void __launch_bounds__(128) lru_chunk_apply_kernel(const LruArgs a) {
 // summed in a fixed order.
 constexpr int SSD_TOK = 8, SSD_NR = 32;
 
-// NR state rows per thread; EXACT: N == NR * NS, so no row needs a bound check (the loop bodies stay branch-free)
-template <int NR, bool EXACT>
-__global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, int NS) {
+// NR state rows per thread; EXACT: N == NR * NS, so no row needs a bound check (the loop bodies stay branch-free).
+// MODE 0 walks a whole segment from the slot's state.  Long portions run in three parallel steps over chunks of SSD_CH
+// tokens (a chunk starts a multiple of SSD_CH rows from its segment's start), as the decay is one number per head and token:
+// MODE 1 runs every chunk from a zero state (local outputs to y, the running product of the decays to ws_cum, the chunk's
+// total decay and end state to ws_p / ws_state), ssd_carry_kernel carries the true state over the chunks (leaving every
+// chunk's incoming state in ws_state), MODE 2 adds C_t^T (cum_t * S_in) to y.  Only the rounding differs from MODE 0.
+constexpr int SSD_CH = 64;
+__device__ __forceinline__ int ssd_chunk_id(int r0, int seg, int k) { return r0 / SSD_CH + seg + k; }  // unique over the batch
+
+template <int NR, bool EXACT, int MODE>
+__global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, int NS, int chunks) {
   extern __shared__ float sm[];
   pdl_wait();
   pdl_trigger();
-  const int seg = blockIdx.x, hd = blockIdx.y, p0 = blockIdx.z * PB;
+  const int seg = blockIdx.x / chunks, ck = blockIdx.x % chunks, hd = blockIdx.y, p0 = blockIdx.z * PB;
   const int N = a.N, P = a.P;
   const int p = threadIdx.x % PB, ns = threadIdx.x / PB;
   const int grp = hd / (a.heads / a.groups);
   float* Bs = sm;                       // [SSD_TOK][N]
   float* Cs = Bs + SSD_TOK * N;         // [SSD_TOK][N]
   float* xs = Cs + SSD_TOK * N;         // [SSD_TOK][PB]
-  float* dts = xs + SSD_TOK * PB;       // [SSD_TOK] dt, then [SSD_TOK] decay
+  float* dts = xs + SSD_TOK * PB;       // [SSD_TOK] dt (MODE 2: cum), then [SSD_TOK] decay
   float* yp = dts + 2 * SSD_TOK;        // [SSD_TOK][NS][PB]
-  const int r0 = a.seg_start[seg], r1 = a.seg_start[seg + 1];
+  const int s0 = a.seg_start[seg], s1 = a.seg_start[seg + 1];
+  const int r0 = MODE == 0 ? s0 : s0 + ck * SSD_CH, r1 = MODE == 0 ? s1 : min(s1, r0 + SSD_CH);
+  if (r0 >= s1) return;
   const bool colok = p0 + p < P;
-  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)hd * N * P;
+  float* sp = MODE == 0 ? a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)hd * N * P
+                        : a.ws_state + ((size_t)ssd_chunk_id(s0, seg, ck) * a.heads + hd) * N * P;
   float S[NR];
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
     const int n = ns + i * NS;
-    S[i] = ((EXACT || n < N) && colok) ? sp[(size_t)n * P + p0 + p] : 0.f;
+    S[i] = (MODE != 1 && (EXACT || n < N) && colok) ? sp[(size_t)n * P + p0 + p] : 0.f;
   }
   const float Dh = bf2f(a.D[hd]), Aneg = -expf(bf2f(a.A_log[hd])), dtb = bf2f(a.dt_bias[hd]);
   const int nthr = blockDim.x;
+  const bool scribe = threadIdx.x == 0 && blockIdx.z == 0;  // writes what is one number per (token, head)
+  float cum = 1.f;
   for (int t0 = r0; t0 < r1; t0 += SSD_TOK) {
     const int nt = min(SSD_TOK, r1 - t0);
     __syncthreads();
     for (int i = threadIdx.x; i < nt * N; i += nthr) {
       const int t = i / N, n = i - t * N;
-      Bs[t * N + n] = a.B[(size_t)(t0 + t) * a.ld + grp * N + n];
+      if (MODE != 2) Bs[t * N + n] = a.B[(size_t)(t0 + t) * a.ld + grp * N + n];
       Cs[t * N + n] = a.C[(size_t)(t0 + t) * a.ld + grp * N + n];
     }
-    for (int i = threadIdx.x; i < nt * PB; i += nthr) {
-      const int t = i / PB, pp = i - t * PB;
-      xs[t * PB + pp] = p0 + pp < P ? a.x[(size_t)(t0 + t) * a.ld + (size_t)hd * P + p0 + pp] : 0.f;
-    }
-    for (int i = threadIdx.x; i < nt; i += nthr) {
-      const float dt = softplusf_(a.dt_raw[(size_t)(t0 + i) * a.ld_dt + hd] + dtb);
-      dts[i] = dt;
-      dts[SSD_TOK + i] = expf(Aneg * dt);
+    if (MODE != 2) {
+      for (int i = threadIdx.x; i < nt * PB; i += nthr) {
+        const int t = i / PB, pp = i - t * PB;
+        xs[t * PB + pp] = p0 + pp < P ? a.x[(size_t)(t0 + t) * a.ld + (size_t)hd * P + p0 + pp] : 0.f;
+      }
+      for (int i = threadIdx.x; i < nt; i += nthr) {
+        const float dt = softplusf_(a.dt_raw[(size_t)(t0 + i) * a.ld_dt + hd] + dtb);
+        dts[i] = dt;
+        dts[SSD_TOK + i] = expf(Aneg * dt);
+      }
+    } else {
+      for (int i = threadIdx.x; i < nt; i += nthr) dts[i] = a.ws_cum[(size_t)(t0 + i) * a.heads + hd];
     }
     __syncthreads();
     for (int t = 0; t < nt; ++t) {
-      const float dt = dts[t], dec = dts[SSD_TOK + t];
-      const float dx = dt * xs[t * PB + p];
       float y = 0.f;
+      if (MODE != 2) {
+        const float dt = dts[t], dec = dts[SSD_TOK + t];
+        const float dx = dt * xs[t * PB + p];
 #pragma unroll
-      for (int i = 0; i < NR; ++i) {
-        const int n = ns + i * NS;
-        if (EXACT || n < N) {
-          S[i] = fmaf(dec, S[i], Bs[t * N + n] * dx);
-          y = fmaf(S[i], Cs[t * N + n], y);
+        for (int i = 0; i < NR; ++i) {
+          const int n = ns + i * NS;
+          if (EXACT || n < N) {
+            S[i] = fmaf(dec, S[i], Bs[t * N + n] * dx);
+            y = fmaf(S[i], Cs[t * N + n], y);
+          }
+        }
+        if (MODE == 1) {
+          cum *= dec;
+          if (scribe) a.ws_cum[(size_t)(t0 + t) * a.heads + hd] = cum;
+        }
+      } else {
+#pragma unroll
+        for (int i = 0; i < NR; ++i) {
+          const int n = ns + i * NS;
+          if (EXACT || n < N) y = fmaf(S[i], Cs[t * N + n], y);
         }
       }
       yp[(t * NS + ns) * PB + p] = y;
@@ -265,14 +294,38 @@ __global__ void __launch_bounds__(512) ssd_scan_kernel(const SsdArgs a, int PB, 
       if (p0 + pp >= P) continue;
       float y = 0.f;
       for (int s = 0; s < NS; ++s) y += yp[(t * NS + s) * PB + pp];
-      a.y[(size_t)(t0 + t) * a.ldy + (size_t)hd * P + p0 + pp] = fmaf(Dh, xs[t * PB + pp], y);
+      float* dst = a.y + (size_t)(t0 + t) * a.ldy + (size_t)hd * P + p0 + pp;
+      if (MODE != 2) *dst = fmaf(Dh, xs[t * PB + pp], y);
+      else *dst = fmaf(dts[t], y, *dst);
     }
   }
+  if (MODE == 2) return;
 #pragma unroll
   for (int i = 0; i < NR; ++i) {
     const int n = ns + i * NS;
     if ((EXACT || n < N) && colok) sp[(size_t)n * P + p0 + p] = S[i];
   }
+  if (MODE == 1 && scribe) a.ws_p[(size_t)ssd_chunk_id(s0, seg, ck) * a.heads + hd] = cum;
+}
+
+// thread (segment, head, state element): S_in of every chunk replaces its local end state; the slot gets the final state
+__global__ void __launch_bounds__(256) ssd_carry_kernel(const SsdArgs a) {
+  pdl_wait();
+  pdl_trigger();
+  const int seg = blockIdx.x, hd = blockIdx.y;
+  const size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x, NP = (size_t)a.N * a.P;
+  if (e >= NP) return;
+  const int s0 = a.seg_start[seg], s1 = a.seg_start[seg + 1];
+  float* sp = a.state + (size_t)a.seg_slot[seg] * a.slot_stride + (size_t)hd * NP + e;
+  float S = *sp;
+  for (int k = 0; s0 + k * SSD_CH < s1; ++k) {
+    const size_t id = (size_t)ssd_chunk_id(s0, seg, k);
+    float* q = a.ws_state + (id * a.heads + hd) * NP + e;
+    const float Q = *q, Pk = a.ws_p[id * a.heads + hd];
+    *q = S;
+    S = fmaf(Pk, S, Q);
+  }
+  *sp = S;
 }
 
 // CTA (row, group)
@@ -339,11 +392,16 @@ cudaError_t launch_lru_scan(const LruArgs& a, cudaStream_t st) {
 cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st) {
   if (a.n_seg <= 0 || a.n_rows <= 0) return cudaSuccess;
   if (a.heads % a.groups) return cudaErrorInvalidValue;
-  // state rows per thread: the smallest of 4 / 8 / 16 / 32 that divides N (branch-free loops, many threads per column),
-  // else 32 with bound checks; the CTA's ~256 threads are NS row slices x PB columns
+  // long portions run chunk-parallel.  Workspace: cum [n_rows, heads] | chunk decays [ids, heads] | chunk states [ids, heads, N, P]
+  const size_t ids = (size_t)a.n_rows / SSD_CH + a.n_seg + 2, NP = (size_t)a.N * a.P;
+  const size_t need = (size_t)a.n_rows * a.heads + ids * a.heads + ids * a.heads * NP;
+  const bool chunked = a.ws && a.n_rows >= 4 * SSD_CH && a.n_seg <= 16 && need <= a.ws_floats;
+  // state rows per thread, a divisor of N out of 4 / 8 / 16 / 32 (branch-free loops), else 32 with bound checks: the smallest
+  // when a segment is walked token by token (many threads per column hide the serial chain), the largest when the chunks
+  // supply the parallelism (fewer partial sums to combine per token); the CTA's ~256 threads are NS row slices x PB columns
   int NR = 0;
   for (int c : {4, 8, 16, 32})
-    if (!NR && a.N % c == 0 && a.N / c <= 64) NR = c;
+    if ((!NR || chunked) && a.N % c == 0 && a.N / c <= 64) NR = c;
   const bool exact = NR != 0;
   if (!exact) NR = SSD_NR;
   const int NS = (a.N + NR - 1) / NR;
@@ -351,21 +409,33 @@ cudaError_t launch_ssd_scan(const SsdArgs& a, cudaStream_t st) {
   int PB = std::max(1, std::min(a.P, std::max(4, 256 / NS)));
   const size_t smem = ((size_t)2 * SSD_TOK * a.N + (size_t)SSD_TOK * PB + 2 * SSD_TOK + (size_t)SSD_TOK * NS * PB) * sizeof(float);
   if (smem > 160 * 1024) return cudaErrorInvalidValue;
-  const dim3 grid(a.n_seg, a.heads, (a.P + PB - 1) / PB), block(PB * NS);
-  auto go = [&](auto kern) {
+  const dim3 block(PB * NS);
+  const int colblocks = (a.P + PB - 1) / PB;
+  auto go = [&](auto kern, const SsdArgs& args, int chunks) {
     if (smem > 48 * 1024) {
       cudaError_t r = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024);
       if (r != cudaSuccess) return r;
     }
-    return launch_k(kern, grid, block, smem, st, a, PB, NS);
+    return launch_k(kern, dim3(args.n_seg * chunks, args.heads, colblocks), block, smem, st, args, PB, NS, chunks);
   };
-  if (!exact) return go(ssd_scan_kernel<SSD_NR, false>);
-  switch (NR) {
-    case 4: return go(ssd_scan_kernel<4, true>);
-    case 8: return go(ssd_scan_kernel<8, true>);
-    case 16: return go(ssd_scan_kernel<16, true>);
-    default: return go(ssd_scan_kernel<32, true>);
+#define SSD_GO(MODE, args, chunks)                                                      \
+  (!exact ? go(ssd_scan_kernel<SSD_NR, false, MODE>, args, chunks)                      \
+          : NR == 4 ? go(ssd_scan_kernel<4, true, MODE>, args, chunks)                  \
+          : NR == 8 ? go(ssd_scan_kernel<8, true, MODE>, args, chunks)                  \
+          : NR == 16 ? go(ssd_scan_kernel<16, true, MODE>, args, chunks) : go(ssd_scan_kernel<32, true, MODE>, args, chunks))
+  if (chunked) {
+    SsdArgs c = a;
+    c.ws_cum = a.ws;
+    c.ws_p = c.ws_cum + (size_t)a.n_rows * a.heads;
+    c.ws_state = c.ws_p + ids * a.heads;
+    const int chunks = (a.n_rows + SSD_CH - 1) / SSD_CH;
+    cudaError_t r = SSD_GO(1, c, chunks);
+    if (r != cudaSuccess) return r;
+    if ((r = launch_k(ssd_carry_kernel, dim3(a.n_seg, a.heads, (unsigned)((NP + 255) / 256)), dim3(256), 0, st, c)) != cudaSuccess) return r;
+    return SSD_GO(2, c, chunks);
   }
+  return SSD_GO(0, a, 1);
+#undef SSD_GO
 }
 
 cudaError_t launch_gated_group_norm(const float* y, int ldy, const float* z, int ldz, const bf16* w, float* out, int ldo, int width, int groups,

@@ -236,12 +236,20 @@ def test_far_key_among_hundreds(tmp_path):
 
 
 def test_long_portions_run_the_chunked_recurrence(tmp_path):
-    # portions of 256 rows and more take the chunk-parallel form of the linear recurrence (chunks of 64 rows from the
+    # portions of 256 rows and more take the chunk-parallel form of both recurrences (chunks of 64 rows from the
     # segment's start, a carry pass); two sequences in one batch, a state carried in from an earlier portion and out to
     # decoded tokens, a decay near one (slow channels) beside fast ones
     cfg = U.make_config([U.parallel_layer(heads=2, kv_heads=1, dim=8, window=9, keep_first=0, width=70, blocks=2, conv=3, left_scale=0.2,
-                                          right_scale=1.5, mlp=U.dense())], width=20, vocab=31, streams=2)
+                                          right_scale=1.5, mlp=U.dense()),
+                         U.mamba_layer(heads=4, vdim=10, state=12, groups=2, norm_groups=1, conv=3),   # state rows divide evenly
+                         U.mamba_layer(heads=2, vdim=70, state=7, groups=1, norm_groups=2, conv=2)],   # bound-checked rows, two column blocks
+                        width=20, vocab=31, streams=2)
     w = U.random_weights(cfg, seed=41)
+    for i in (1, 2):  # slow heads: exp(A) dt small, the state remembers hundreds of tokens
+        bits, al = w[f"l{i}.mix.A_log"]
+        al = al.copy()
+        al[0] = -6.0
+        w[f"l{i}.mix.A_log"] = U.bf16_round(al.astype(np.float32))
     bits, lam = w["l0.mix.right.lam"]
     lam = lam.copy()
     lam[:10] = -9.0  # softplus ~ 1e-4: a stays within 1e-3 of one, the state remembers hundreds of tokens
